@@ -1,0 +1,379 @@
+"""TEST INFRASTRUCTURE ONLY: numpy/ctypes front end of the CPU oracle (liboracle.so, built from qtip_oracle.c) and,
+when present, of the reference's own CPU code compiled in place (_ref/libqtip_ref_{encode,decode}.so).
+
+Only the test suite, the smoke check and the CPU-baseline leg of the benchmark may import this module. The
+product package never does.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
+_u32p = np.ctypeslib.ndpointer(np.uint32, flags="C_CONTIGUOUS")
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+_f64p = np.ctypeslib.ndpointer(np.float64, flags="C_CONTIGUOUS")
+_i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+_i8p = np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS")
+_u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+
+
+def build(ref=False):
+    """Compile the oracle (and, with ref=True and the reference tree present, the reference's CPU code)."""
+    subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
+    if ref and os.path.isdir("/root/reference/src"):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref"], stderr=subprocess.DEVNULL)
+
+
+def _load(path):
+    return C.CDLL(path) if os.path.exists(path) else None
+
+
+def _opt(a, ptr_type=None):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class Oracle:
+    """The plain-C restatement."""
+
+    def __init__(self):
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        L = self.lib = C.CDLL(path)
+        L.qo_f16_to_f32.restype = C.c_float
+        L.qo_f16_to_f32.argtypes = [C.c_uint16]
+        L.qo_f32_to_f16.restype = C.c_uint16
+        L.qo_f32_to_f16.argtypes = [C.c_float]
+        L.qo_build_lut.argtypes = [_u16p, _u32p, C.POINTER(C.c_double)]
+        L.qo_runtime_codebook.argtypes = [_u16p, _f32p, _f32p, _u32p]
+        L.qo_perm.argtypes = [_i32p, _i32p]
+        L.qo_viterbi_fwd.argtypes = [_f32p, C.c_void_p, C.c_int, C.c_int, _u16p, _u16p, _u32p]
+        L.qo_viterbi_overlap.argtypes = [_u16p, _u16p, C.c_int, _i32p]
+        L.qo_viterbi_finish.argtypes = [_u16p, _u16p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p,
+                                        C.c_long, C.c_int, _u32p]
+        L.qo_decode_states.argtypes = [_u16p, C.c_int, _f32p, _u32p]
+        L.qo_quantize_tiles.argtypes = [_f32p, C.c_int, _u32p, C.c_void_p, C.c_void_p]
+        L.qo_quantize_seq_ref.argtypes = [_f32p, C.c_int, _u32p, _u16p, C.c_void_p, C.c_void_p]
+        L.qo_path_cost.restype = C.c_double
+        L.qo_path_cost.argtypes = [_f32p, _u16p, _u32p]
+        L.qo_pack_trellis.argtypes = [_u16p, C.c_long, _u16p]
+        L.qo_unpack_trellis.argtypes = [_u16p, C.c_long, _u16p]
+        L.qo_swizzle.argtypes = [_u16p, C.c_int, C.c_int, _u16p]
+        L.qo_unswizzle.argtypes = [_u16p, C.c_int, C.c_int, _u16p]
+        L.qo_had_table.argtypes = [C.c_int, _i8p]
+        L.qo_had_K.argtypes = [C.c_int]
+        L.qo_hadamard_rows_ref.argtypes = [_f64p, C.c_long, C.c_int, C.c_long, C.c_int]
+        L.qo_ldlq_prep.argtypes = [_f32p, _f32p, _f32p, _f32p, C.c_long, C.c_long, C.c_int, C.c_int, _f32p]
+        L.qo_ldlq_f32.argtypes = [_f32p, _f32p, C.c_long, C.c_long, _f32p, _u16p, _u32p]
+        L.qo_ldlq_ref.argtypes = [_f32p, _f32p, C.c_int, C.c_int, _f32p, _u16p, _u32p]
+        L.qo_block_ldl.argtypes = [_f64p, C.c_int, _f32p]
+        L.qo_decode_rows.argtypes = [_u16p, C.c_int, C.c_int, _f32p, _f32p, C.c_int, C.c_int, _f32p]
+        L.qo_rt_hadamard.argtypes = [_f64p, C.c_int, C.c_int]
+        L.qo_reference_forward.argtypes = [_u16p, _f32p, _f32p, _u16p, C.c_int, C.c_int, _f32p, C.c_int, C.c_int,
+                                           C.c_int, _f32p, C.c_void_p]
+        L.qo_fp8_forward.argtypes = [_u8p, _f32p, C.c_int, C.c_int, _f32p, C.c_int, C.c_int, _f32p]
+
+    # ---- codebook
+    def build_lut(self, tlut_h):
+        tlut_h = np.ascontiguousarray(tlut_h, np.uint16).reshape(-1)
+        assert tlut_h.size == 1024
+        lut = np.empty(65536, np.uint32)
+        rms = C.c_double()
+        self.lib.qo_build_lut(tlut_h, lut, C.byref(rms))
+        return lut, rms.value
+
+    def runtime_codebook(self, tlut_h):
+        tlut_h = np.ascontiguousarray(tlut_h, np.uint16).reshape(-1)
+        c0, c1, b2 = np.empty(1024, np.float32), np.empty(1024, np.float32), np.empty(1024, np.uint32)
+        if self.lib.qo_runtime_codebook(tlut_h, c0, c1, b2):
+            raise ValueError("non-finite tlut entry")
+        return c0, c1, b2
+
+    def perm(self):
+        p, i = np.empty(256, np.int32), np.empty(256, np.int32)
+        self.lib.qo_perm(p, i)
+        return p, i
+
+    # ---- exact Viterbi (kernel arithmetic)
+    def viterbi_fwd(self, X, overlap, roll, lut):
+        X = np.ascontiguousarray(X, np.float32).reshape(-1, 256)
+        B = X.shape[0]
+        A = np.empty((B, 127, 1024), np.uint16)
+        fs = np.empty(B, np.uint16)
+        ov = None if overlap is None else np.ascontiguousarray(overlap, np.int32)
+        self.lib.qo_viterbi_fwd(X, _opt(ov), int(roll), B, A, fs, lut)
+        return A, fs
+
+    def viterbi_overlap(self, A, fs):
+        B = fs.shape[0]
+        ov = np.empty(B, np.int32)
+        self.lib.qo_viterbi_overlap(A, fs, B, ov)
+        return ov
+
+    def viterbi_finish(self, A, fs, lut, b0=0, nblk=1, blk=0, Q=None, hatWT=None, m=0, col0=0):
+        B = fs.shape[0]
+        if Q is None:
+            Q = np.zeros(((b0 + B) * nblk, 128), np.uint16)
+        self.lib.qo_viterbi_finish(A, fs, B, b0, _opt(Q), nblk, blk, _opt(hatWT), m, col0, lut)
+        return Q
+
+    def decode_states(self, states, lut):
+        states = np.ascontiguousarray(states, np.uint16).reshape(-1, 128)
+        hat = np.empty((states.shape[0], 256), np.float32)
+        self.lib.qo_decode_states(states, states.shape[0], hat, lut)
+        return hat
+
+    def quantize_tiles(self, X, lut):
+        X = np.ascontiguousarray(X, np.float32).reshape(-1, 256)
+        B = X.shape[0]
+        st, hat = np.empty((B, 128), np.uint16), np.empty((B, 256), np.float32)
+        self.lib.qo_quantize_tiles(X, B, lut, _opt(st), _opt(hat))
+        return st, hat
+
+    # ---- fp64 Viterbi
+    def quantize_seq_ref(self, X, lut):
+        X = np.ascontiguousarray(X, np.float32).reshape(-1, 256)
+        B = X.shape[0]
+        st, hat, cost = np.empty((B, 128), np.uint16), np.empty((B, 256), np.float32), np.empty(B, np.float64)
+        self.lib.qo_quantize_seq_ref(X, B, lut, st, _opt(hat), _opt(cost))
+        return st, hat, cost
+
+    def path_cost(self, x, states, lut):
+        return self.lib.qo_path_cost(np.ascontiguousarray(x, np.float32), np.ascontiguousarray(states, np.uint16), lut)
+
+    # ---- packing
+    def pack(self, states):
+        states = np.ascontiguousarray(states, np.uint16).reshape(-1, 128)
+        out = np.empty((states.shape[0], 32), np.uint16)
+        self.lib.qo_pack_trellis(states, states.shape[0], out)
+        return out
+
+    def unpack(self, packed):
+        packed = np.ascontiguousarray(packed, np.uint16).reshape(-1, 32)
+        out = np.empty((packed.shape[0], 128), np.uint16)
+        self.lib.qo_unpack_trellis(packed, packed.shape[0], out)
+        return out
+
+    def swizzle(self, packed, m, n):
+        packed = np.ascontiguousarray(packed, np.uint16)
+        out = np.empty_like(packed)
+        if self.lib.qo_swizzle(packed, m, n, out):
+            raise ValueError("kernel layout needs m, n multiples of 32")
+        return out
+
+    def unswizzle(self, words, m, n):
+        words = np.ascontiguousarray(words, np.uint16)
+        out = np.empty_like(words)
+        if self.lib.qo_unswizzle(words, m, n, out):
+            raise ValueError("kernel layout needs m, n multiples of 32")
+        return out
+
+    # ---- Hadamard
+    def had_table(self, K):
+        H = np.empty((K, K), np.int8)
+        if self.lib.qo_had_table(K, H):
+            raise ValueError("no table of order %d" % K)
+        return H
+
+    def had_K(self, n):
+        return self.lib.qo_had_K(n)
+
+    def hadamard_rows(self, X, transpose):
+        X = np.array(X, np.float64, order="C")
+        X2 = X.reshape(-1, X.shape[-1])
+        if self.lib.qo_hadamard_rows_ref(X2, X2.shape[0], X2.shape[1], X2.shape[1], int(transpose)):
+            raise ValueError("unsupported Hadamard size")
+        return X
+
+    # ---- LDLQ
+    def ldlq_prep(self, WT, hatWT, prod, L, col0, bufend):
+        n, m = WT.shape
+        X = np.empty((m // 16, 256), np.float32)
+        self.lib.qo_ldlq_prep(WT, hatWT, prod, L, n, m, col0, bufend, X)
+        return X
+
+    def ldlq_f32(self, WT, L, lut):
+        WT = np.ascontiguousarray(WT, np.float32)
+        L = np.ascontiguousarray(L, np.float32)
+        n, m = WT.shape
+        hat = np.empty((n, m), np.float32)
+        Q = np.empty(((m // 16) * (n // 16), 128), np.uint16)
+        if self.lib.qo_ldlq_f32(WT, L, n, m, hat, Q, lut):
+            raise ValueError("LDLQ needs n % 128 == 0 and m % 16 == 0")
+        return hat, Q
+
+    def ldlq_ref(self, Wr, L, lut):
+        Wr = np.ascontiguousarray(Wr, np.float32)
+        L = np.ascontiguousarray(L, np.float32)
+        m, n = Wr.shape
+        hat = np.empty((m, n), np.float32)
+        Q = np.empty(((m // 16) * (n // 16), 128), np.uint16)
+        if self.lib.qo_ldlq_ref(Wr, L, m, n, hat, Q, lut):
+            raise ValueError("LDLQ needs n % 128 == 0 and m % 16 == 0")
+        return hat, Q
+
+    def block_ldl(self, H):
+        A = np.array(H, np.float64, order="C")
+        n = A.shape[0]
+        L = np.empty((n, n), np.float32)
+        rc = self.lib.qo_block_ldl(A, n, L)
+        if rc:
+            raise ValueError("block LDL failed (%d)" % rc)
+        return L
+
+    # ---- decode side
+    def decode_rows(self, trellis, n_in, n_out, tlut_h, row0, rows, bf16):
+        c0, c1, b2 = self.runtime_codebook(tlut_h)
+        if bf16:
+            c0 = ((b2 & 0xFFFF) << 16).astype(np.uint32).view(np.float32)
+            c1 = (b2 & 0xFFFF0000).astype(np.uint32).view(np.float32)
+        w = np.empty((rows, n_in), np.float32)
+        if self.lib.qo_decode_rows(np.ascontiguousarray(trellis, np.uint16).reshape(-1), n_in, n_out,
+                                   np.ascontiguousarray(c0), np.ascontiguousarray(c1), row0, rows, w):
+            raise ValueError("decode rows must be whole 16-row tiles")
+        return w
+
+    def rt_hadamard(self, x, transpose):
+        x = np.array(x, np.float64, order="C")
+        if self.lib.qo_rt_hadamard(x, x.size, int(transpose)):
+            raise ValueError("unsupported Hadamard size")
+        return x
+
+    def reference_forward(self, trellis, su, sv, tlut_h, n_in, n_out, x, device_rounding=False, round_z=False,
+                          want_z=False):
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, n_in)
+        rows = x.shape[0]
+        y = np.empty((rows, n_out), np.float32)
+        z = np.empty((rows, n_out), np.float32) if want_z else None
+        rc = self.lib.qo_reference_forward(np.ascontiguousarray(trellis, np.uint16).reshape(-1),
+                                           np.ascontiguousarray(su, np.float32), np.ascontiguousarray(sv, np.float32),
+                                           np.ascontiguousarray(tlut_h, np.uint16).reshape(-1), n_in, n_out, x, rows,
+                                           int(device_rounding), int(round_z), y, _opt(z))
+        if rc:
+            raise ValueError("reference_forward failed")
+        return (y, z) if want_z else y
+
+    def fp8_forward(self, w, scale, x, device_rounding=True):
+        w = np.ascontiguousarray(w, np.uint8)
+        n_out, n_in = w.shape
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, n_in)
+        y = np.empty((x.shape[0], n_out), np.float32)
+        self.lib.qo_fp8_forward(w, np.ascontiguousarray(scale, np.float32), n_in, n_out, x, x.shape[0],
+                                int(device_rounding), y)
+        return y
+
+
+class Reference:
+    """The reference's own CPU code compiled in place. `available` is False when the prebuilt files are absent."""
+
+    def __init__(self):
+        self.enc = _load(os.path.join(_HERE, "_ref", "libqtip_ref_encode.so"))
+        self.dec = _load(os.path.join(_HERE, "_ref", "libqtip_ref_decode.so"))
+        self.available = self.enc is not None and self.dec is not None
+        if self.enc is not None:
+            E = self.enc
+            E.ref_codebook.argtypes = [_u16p, _u32p, C.POINTER(C.c_double)]
+            E.ref_perm.argtypes = [_i32p, _i32p]
+            E.ref_had_table.argtypes = [C.c_int, _i8p]
+            E.ref_hadamard_rows.argtypes = [_f64p, C.c_long, C.c_int, C.c_long, C.c_int]
+            E.ref_quantize_seqs.argtypes = [_f32p, C.c_int, _u16p, C.c_void_p, C.c_void_p]
+            E.ref_path_cost.restype = C.c_double
+            E.ref_path_cost.argtypes = [_f32p, _u16p]
+            E.ref_pack_trellis.argtypes = [_u16p, C.c_long, _u16p]
+            E.ref_unpack_trellis.argtypes = [_u16p, C.c_long, _u16p]
+            E.ref_swizzle.argtypes = [_u16p, C.c_int, C.c_int, _u16p]
+            E.ref_unswizzle.argtypes = [_u16p, C.c_int, C.c_int, _u16p]
+            E.ref_block_ldl.argtypes = [_f64p, C.c_int, _f32p, C.c_int]
+        if self.dec is not None:
+            D = self.dec
+            D.rref_codebook.argtypes = [_u16p, _f32p, _f32p, _u32p]
+            D.rref_hadamard.argtypes = [_f64p, C.c_int, C.c_int]
+            D.rref_decode_rows.argtypes = [_u16p, _u16p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _f32p]
+            D.rref_forward.argtypes = [_u16p, _f32p, _f32p, _u16p, C.c_int, C.c_int, _f32p, C.c_int, C.c_int, C.c_int,
+                                       _f32p]
+
+    def codebook(self):
+        """(tlut fp16 bits [512,2], lut_h2 [65536], lut_rms) of the reference's committed HYB code."""
+        t, l, r = np.empty(1024, np.uint16), np.empty(65536, np.uint32), C.c_double()
+        self.enc.ref_codebook(t, l, C.byref(r))
+        return t.reshape(512, 2), l, r.value
+
+    def perm(self):
+        p, i = np.empty(256, np.int32), np.empty(256, np.int32)
+        self.enc.ref_perm(p, i)
+        return p, i
+
+    def had_table(self, K):
+        H = np.empty((K, K), np.int8)
+        return H if self.enc.ref_had_table(K, H) else None
+
+    def hadamard_rows(self, X, transpose):
+        X = np.array(X, np.float64, order="C")
+        X2 = X.reshape(-1, X.shape[-1])
+        self.enc.ref_hadamard_rows(X2, X2.shape[0], X2.shape[1], X2.shape[1], int(transpose))
+        return X
+
+    def quantize_seqs(self, X):
+        X = np.ascontiguousarray(X, np.float32).reshape(-1, 256)
+        B = X.shape[0]
+        st, hat, cost = np.empty((B, 128), np.uint16), np.empty((B, 256), np.float32), np.empty(B, np.float64)
+        self.enc.ref_quantize_seqs(X, B, st, _opt(hat), _opt(cost))
+        return st, hat, cost
+
+    def pack(self, states):
+        states = np.ascontiguousarray(states, np.uint16).reshape(-1, 128)
+        out = np.empty((states.shape[0], 32), np.uint16)
+        self.enc.ref_pack_trellis(states, states.shape[0], out)
+        return out
+
+    def unpack(self, packed):
+        packed = np.ascontiguousarray(packed, np.uint16).reshape(-1, 32)
+        out = np.empty((packed.shape[0], 128), np.uint16)
+        self.enc.ref_unpack_trellis(packed, packed.shape[0], out)
+        return out
+
+    def swizzle(self, packed, m, n):
+        packed = np.ascontiguousarray(packed, np.uint16)
+        out = np.empty_like(packed)
+        self.enc.ref_swizzle(packed, m, n, out)
+        return out
+
+    def block_ldl(self, H, threads=4):
+        A = np.array(H, np.float64, order="C")
+        L = np.empty(A.shape, np.float32)
+        if self.enc.ref_block_ldl(A, A.shape[0], L, threads):
+            raise ValueError("block LDL failed")
+        return L
+
+    def runtime_codebook(self, tlut_h):
+        c0, c1, b2 = np.empty(1024, np.float32), np.empty(1024, np.float32), np.empty(1024, np.uint32)
+        if self.dec.rref_codebook(np.ascontiguousarray(tlut_h, np.uint16).reshape(-1), c0, c1, b2):
+            raise ValueError("make_codebook failed")
+        return c0, c1, b2
+
+    def rt_hadamard(self, x, transpose):
+        x = np.array(x, np.float64, order="C")
+        if self.dec.rref_hadamard(x, x.size, int(transpose)):
+            raise ValueError("unsupported Hadamard size")
+        return x
+
+    def decode_rows(self, trellis, n_in, n_out, tlut_h, row0, rows, bf16):
+        w = np.empty((rows, n_in), np.float32)
+        if self.dec.rref_decode_rows(np.ascontiguousarray(trellis, np.uint16).reshape(-1),
+                                     np.ascontiguousarray(tlut_h, np.uint16).reshape(-1), n_in, n_out, row0, rows,
+                                     int(bf16), w):
+            raise ValueError("decode_rows failed")
+        return w
+
+    def reference_forward(self, trellis, su, sv, tlut_h, n_in, n_out, x, device_rounding=False, round_z=False):
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, n_in)
+        y = np.empty((x.shape[0], n_out), np.float32)
+        if self.dec.rref_forward(np.ascontiguousarray(trellis, np.uint16).reshape(-1),
+                                 np.ascontiguousarray(su, np.float32), np.ascontiguousarray(sv, np.float32),
+                                 np.ascontiguousarray(tlut_h, np.uint16).reshape(-1), n_in, n_out, x, x.shape[0],
+                                 int(device_rounding), int(round_z), y):
+            raise ValueError("reference_forward failed")
+        return y
