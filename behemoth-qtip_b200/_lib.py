@@ -1,0 +1,116 @@
+"""ctypes binding of libqtip_b200.so: one Python function per C-ABI entry point of include/qtip_b200.h.
+
+The library is the product; there is no Python or CPU fallback. Loading fails loudly when the shared library is
+missing, and every call raises QtipError with the library's message on a non-zero status.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libqtip_b200.so")
+
+
+class QtipError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__("qtip_b200 status %d: %s" % (code, message))
+        self.code = code
+
+
+class QtipMatrix(C.Structure):
+    """POD mirror of qtip_matrix (QtipMatrix of the reference runtime): device pointers + geometry."""
+    _fields_ = [("trellis", C.c_void_p), ("su", C.c_void_p), ("sv", C.c_void_p), ("lut", C.c_void_p),
+                ("n_in", C.c_int), ("n_out", C.c_int)]
+
+
+_P, _I, _L, _Z, _F = C.c_void_p, C.c_int, C.c_long, C.c_size_t, C.c_float
+
+# name -> argument types; every function returns int except where noted in _RESTYPES
+SIGNATURES = {
+    "qtip_init": [],
+    "qtip_encoder_lut": [_P, _P, C.POINTER(C.c_double), _P],
+    "qtip_runtime_lut": [_P, _P, _P],
+    "qtip_k_ldlq_prep": [_P, _P, _P, _P, _L, _L, _I, _I, _P, _P],
+    "qtip_k_viterbi_fwd": [_P, _P, _I, _I, _P, _P, _P, _P],
+    "qtip_k_viterbi_overlap": [_P, _P, _I, _P, _P],
+    "qtip_k_viterbi_finish": [_P, _P, _I, _I, _P, _I, _I, _P, _L, _I, _P, _P],
+    "qtip_k_decode_states": [_P, _I, _P, _P, _P],
+    "qtip_k_hadamard_rows": [_P, _L, _I, _L, _I, _P],
+    "qtip_k_transpose": [_P, _L, _L, _L, _P, _L, _P],
+    "qtip_k_scale_rows_cols": [_P, _L, _L, _L, _P, _P, _P],
+    "qtip_k_scale": [_P, _L, _L, _L, _F, _P],
+    "qtip_k_sub": [_P, _P, _P, _L, _L, _L, _P],
+    "qtip_k_sumsq": [_P, _L, _L, _L, _P, _P],
+    "qtip_k_dot": [_P, _L, _P, _L, _L, _L, _P, _P],
+    "qtip_k_add_diag": [_P, _L, _F, _P],
+    "qtip_k_diag_sum": [_P, _L, _P, _P],
+    "qtip_k_split_bf16": [_P, _L, _L, _L, _P, _P, _L, _P],
+    "qtip_k_diff_split_bf16": [_P, _P, _L, _L, _L, _P, _P, _L, _P],
+    "qtip_quantize_tiles": [_P, _I, _P, _P, _P, _P, _Z, _P],
+    "qtip_quantize_tiles_scatter": [_P, _I, _I, _P, _P, _I, _I, _P, _L, _I, _P, _Z, _P],
+    "qtip_workspace_status": [_P, _P],
+    "qtip_k_viterbi_fwd_words": [_P, _P, _I, _I, _P, _I, _P, _P, _P, _P],
+    "qtip_k_viterbi_overlap_words": [_P, _P, _I, _P, _P],
+    "qtip_k_viterbi_finish_words": [_P, _P, _I, _I, _P, _I, _I, _P, _P, _L, _I, _P, _P],
+    "qtip_tiles_from_matrix": [_P, _L, _L, _L, _P, _P],
+    "qtip_ldlq": [_P, _P, _L, _L, _L, _L, _P, _P, _P, _P, _Z, _P],
+    "qtip_pack_trellis": [_P, _L, _P, _P],
+    "qtip_unpack_trellis": [_P, _L, _P, _P],
+    "qtip_swizzle_for_kernel": [_P, _I, _I, _P, _P],
+    "qtip_unswizzle_for_kernel": [_P, _I, _I, _P, _P],
+    "qtip_prepare": [QtipMatrix, _P, _P, _P, _P, _I, _I],
+    "qtip_multiply": [QtipMatrix, _P, _P, _I, _I, _P, _I],
+    "qtip_finish": [QtipMatrix, _P, _P, _P, _I, _I, _P, _I, _I],
+    "qtip_finish_b16": [QtipMatrix, _P, _P, _P, _I, _P, _I],
+    "qtip_forward": [QtipMatrix, _P, _P, _P, _P, _P, _I, _P, _I],
+    "qtip_multiply_batch": [QtipMatrix, _P, _P, _I, _I, _I, _P, _I],
+    "qtip_decode_matrix": [QtipMatrix, _P, _P],
+    "qtip_reduce_products": [_P, _Z, _I, _P],
+    "qtip_reduce_to_b16": [_P, _P, _P, _Z, _I, _I, _P],
+}
+_RESTYPES = {
+    "qtip_last_error": (C.c_char_p, []),
+    "qtip_abi_version": (C.c_int, []),
+    "qtip_quantize_workspace_bytes": (C.c_size_t, [_I]),
+    "qtip_ldlq_workspace_bytes": (C.c_size_t, [_L, _L]),
+}
+
+
+def exported_names():
+    return sorted(list(SIGNATURES) + list(_RESTYPES))
+
+
+class Library:
+    def __init__(self, path=LIB_PATH):
+        if not os.path.exists(path):
+            raise ImportError("%s is missing: build it with `python behemoth-qtip_b200/build.py` (needs nvcc); "
+                              "there is no CPU fallback" % path)
+        self.cdll = C.CDLL(path)
+        for name, args in SIGNATURES.items():
+            fn = getattr(self.cdll, name)
+            fn.restype = C.c_int
+            fn.argtypes = args
+        for name, (res, args) in _RESTYPES.items():
+            fn = getattr(self.cdll, name)
+            fn.restype = res
+            fn.argtypes = args
+
+    def last_error(self):
+        return self.cdll.qtip_last_error().decode()
+
+    def call(self, name, *args):
+        rc = getattr(self.cdll, name)(*args)
+        if rc != 0:
+            raise QtipError(rc, self.last_error())
+
+    def raw(self, name):
+        return getattr(self.cdll, name)
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = Library()
+    return _lib

@@ -1,0 +1,73 @@
+// Shared helpers of the qtip_b200 library: status/error plumbing, per-device state, small device functions.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../../include/qtip_b200.h"
+
+namespace qb {
+
+// Sets the calling thread's error message and returns `code`.
+int fail(int code, const char* fmt, ...);
+// Records a CUDA failure; returns the (positive) cudaError_t value.
+int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
+
+#define QB_CUDA(x)                                                        \
+  do {                                                                    \
+    cudaError_t e_ = (x);                                                 \
+    if (e_ != cudaSuccess) return qb::cuda_fail(e_, #x, __FILE__, __LINE__); \
+  } while (0)
+#define QB_LAUNCHED() QB_CUDA(cudaGetLastError())
+#define QB_REQUIRE(cond, code, ...)                   \
+  do {                                                \
+    if (!(cond)) return qb::fail(code, __VA_ARGS__); \
+  } while (0)
+
+inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+
+// Per-device facts filled by qtip_init().
+struct DeviceInfo {
+  bool ready = false;
+  int sm_count = 0;
+  int max_clusters = 0;  // co-resident 8-CTA clusters of the Viterbi kernel
+};
+DeviceInfo* device_info();  // for the current device; nullptr + error set if qtip_init() has not run there
+int viterbi_device_setup(DeviceInfo* info);  // viterbi.cu
+int decode_device_setup(DeviceInfo* info);   // decode.cu
+int hadamard_device_setup();                 // hadamard.cu: uploads the order-12/20/28 factors
+
+// Order-K Hadamard factor (Paley construction), K in {12, 20, 28}; row-major +-1. Returns false otherwise.
+bool had_factor(int K, int8_t* H);
+// get_hadK restricted to the carried orders: 12, 20, 28, 1 (power of two) or 0 (unsupported).
+int had_order(long n);
+
+// ---- device helpers
+__device__ __forceinline__ float bf16_to_f32(uint16_t x) { return __uint_as_float(uint32_t(x) << 16); }
+__device__ __forceinline__ uint16_t f32_to_bf16(float x) {  // round to nearest even, finite inputs
+  uint32_t u = __float_as_uint(x);
+  return uint16_t((u + 0x7fffu + ((u >> 16) & 1u)) >> 16);
+}
+__device__ __forceinline__ float half_lo(uint32_t u) { return __half2float(__ushort_as_half(uint16_t(u))); }
+__device__ __forceinline__ float half_hi(uint32_t u) { return __half2float(__ushort_as_half(uint16_t(u >> 16))); }
+__device__ __forceinline__ float round_half(float x) { return __half2float(__float2half_rn(x)); }
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+// Tile permutation: sequence position p <-> tile index 16 r + c.
+__device__ __forceinline__ int perm_fwd(int p) {
+  return ((p >> 1) & 1) * 128 + ((p >> 5) & 7) * 16 + ((p >> 2) & 1) * 8 + ((p >> 3) & 3) * 2 + (p & 1);
+}
+__device__ __forceinline__ int perm_inv(int q) {
+  return ((((((q >> 4) & 7) * 4 + ((q >> 1) & 3)) * 2 + ((q >> 3) & 1)) * 2 + (q >> 7)) * 2) + (q & 1);
+}
+// LUT entry (sign << 9 | index) of a trellis state; bits above 15 are ignored.
+__device__ __forceinline__ uint32_t lut_entry(uint32_t s) {
+  s &= 0xffffu;
+  return ((s * (s + 1u)) >> 6) & 1023u;
+}
+
+inline unsigned blocks_for(long n, int per) { return unsigned((n + per - 1) / per); }
+
+}  // namespace qb

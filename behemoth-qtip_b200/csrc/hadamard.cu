@@ -1,0 +1,267 @@
+// Random-Hadamard transforms x <- (hadK^(T) (x) H_P) x / sqrt(n), n = K * P, K in {1, 12, 20, 28}, P a power of two.
+//
+// (hadK (x) H_P) = (I (x) H_P)(hadK (x) I): the order-K mix across the K chunks is done first, then a natural-order
+// fast Walsh-Hadamard transform on each chunk of P. Every variant below uses that order and the same summation order,
+// so the whole-row kernel and the chunk-per-CTA kernel give identical bits.
+//
+//  * had_row_kernel: one CTA per row, the whole row (up to 57,344 floats = 224 KiB) in shared memory, read and written
+//    once. Used for the quantizer's fp32 matrices and for prefill-sized token batches.
+//  * had_chunk_kernel: K CTAs per row, each mixing its own chunk from the full row (served by L2) and transforming it.
+//    No inter-CTA step; used for a few tokens where latency, not traffic, decides.
+//
+// Sources/destinations (Mode): fp32 in place (quantizer); bf16 x times SU -> bf16 (operator input); fp32 partial
+// products summed over K-splits, optionally rounded to bf16 -> times SV -> bf16 (operator output); bf16 z -> same.
+#include <cmath>
+
+#include "common.cuh"
+
+namespace qb {
+
+// ---- compile-time signs of the order-12/20 (Paley I) and order-28 (Paley II) factors
+__host__ __device__ constexpr int chi_c(int a, int p) {
+  a = ((a % p) + p) % p;
+  if (a == 0) return 0;
+  for (int x = 1; x < p; ++x)
+    if ((x * x) % p == a) return 1;
+  return -1;
+}
+template <int K>
+__host__ __device__ constexpr int had_sign(int i, int j) {
+  if constexpr (K == 1) {
+    return 1;
+  } else if constexpr (K == 12 || K == 20) {
+    constexpr int q = K - 1;
+    if (i == 0) return j == 0 ? 1 : -1;
+    if (j == 0) return 1;
+    const int k = ((j - i) % q + q) % q;
+    return k == 0 ? 1 : -chi_c(k, q);
+  } else {
+    static_assert(K == 28, "unsupported Hadamard order");
+    constexpr int q = 13, h = 14;
+    const int bi = i / h, bj = j / h, r = i % h, c = j % h;
+    const bool core = r >= 1 && c >= 1;
+    const int k = ((c - r) % q + q) % q;
+    const int x = (core && k != 0) ? chi_c(k, q) : 0;
+    if (bi == 0 && bj == 0) return !core ? 1 : (k == 0 ? 1 : x);
+    if (bi != bj) return r == 0 ? (c == 0 ? -1 : 1) : (c == 0 ? 1 : (k == 0 ? -1 : x));
+    return !core ? -1 : (k == 0 ? -1 : -x);
+  }
+}
+// Sign masks: bit k of kRowMask<K,T>[r] is set where the mixing matrix entry (r, k) is -1 (T: transposed factor).
+template <int K, bool T>
+struct SignMasks {
+  uint32_t m[K];
+  constexpr SignMasks() : m{} {
+    for (int r = 0; r < K; ++r) {
+      uint32_t v = 0;
+      for (int k = 0; k < K; ++k)
+        if ((T ? had_sign<K>(k, r) : had_sign<K>(r, k)) < 0) v |= 1u << k;
+      m[r] = v;
+    }
+  }
+};
+
+enum class Mode { F32Inplace, Prepare, Finish, FinishB16 };
+
+struct HadArgs {
+  const void* src;    // fp32 or bf16
+  void* dst;          // fp32 (in place) or bf16
+  const float* sign;  // SU (Prepare) or SV (Finish*), else null
+  long ld;            // row stride of src/dst in elements
+  long split_stride;  // Finish: elements between K-split partials
+  int n, P;
+  int splits, round_z;
+  int ranks;  // > 1: the source is gathered rank-major, [rank][row][n / ranks]
+  int rows;
+  float scale;
+};
+
+template <Mode M>
+__device__ __forceinline__ float load_src(const HadArgs& a, long row, int j) {
+  long at = row * a.ld + j;
+  if (a.ranks > 1) {
+    const int part = a.n / a.ranks, r = j / part;
+    at = (long(r) * a.rows + row) * part + (j - r * part);
+  }
+  if constexpr (M == Mode::F32Inplace) {
+    return static_cast<const float*>(a.src)[at];
+  } else if constexpr (M == Mode::Prepare) {
+    return bf16_to_f32(static_cast<const uint16_t*>(a.src)[at]) * a.sign[j];
+  } else if constexpr (M == Mode::Finish) {
+    const float* z = static_cast<const float*>(a.src);
+    float v = z[at];
+    for (int p = 1; p < a.splits; ++p) v += z[size_t(p) * a.split_stride + at];
+    if (a.round_z) v = bf16_to_f32(f32_to_bf16(v));
+    return v;
+  } else {
+    return bf16_to_f32(static_cast<const uint16_t*>(a.src)[at]);
+  }
+}
+template <Mode M>
+__device__ __forceinline__ void store_dst(const HadArgs& a, long row, int j, float v) {
+  const long at = row * a.ld + j;
+  if constexpr (M == Mode::F32Inplace) {
+    static_cast<float*>(a.dst)[at] = v * a.scale;
+  } else if constexpr (M == Mode::Prepare) {
+    static_cast<uint16_t*>(a.dst)[at] = f32_to_bf16(v * a.scale);
+  } else {
+    static_cast<uint16_t*>(a.dst)[at] = f32_to_bf16(v * a.scale * a.sign[j]);
+  }
+}
+
+// Natural-order FWHT on `count` contiguous chunks of P floats in shared memory. All threads of the CTA take part.
+__device__ __forceinline__ void fwht_shared(float* a, int P, int count) {
+  const int half = (P * count) >> 1;
+  for (int h = 1; h < P; h <<= 1) {
+    for (int t = threadIdx.x; t < half; t += blockDim.x) {
+      const int i = ((t / h) * (2 * h)) + (t % h);  // chunks are multiples of 2h, so this never straddles two chunks
+      const float v = a[i], w = a[i + h];
+      a[i] = v + w;
+      a[i + h] = v - w;
+    }
+    __syncthreads();
+  }
+}
+
+// Mixed value of chunk r at column i: sum over k (ascending) of +-v[k].
+template <int K>
+__device__ __forceinline__ float mix_row(const float (&v)[K], uint32_t mask) {
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < K; ++k) s += __uint_as_float(__float_as_uint(v[k]) ^ (((mask >> k) & 1u) << 31));
+  return s;
+}
+
+template <int K, bool T, Mode M>
+__global__ __launch_bounds__(1024) void had_row_kernel(HadArgs a) {
+  extern __shared__ float row_s[];
+  constexpr SignMasks<K, T> masks{};
+  const long row = blockIdx.x;
+  const int P = a.P;
+  if constexpr (K == 1) {
+    for (int i = threadIdx.x; i < P; i += blockDim.x) row_s[i] = load_src<M>(a, row, i);
+  } else {
+    for (int i = threadIdx.x; i < P; i += blockDim.x) {
+      float v[K];
+#pragma unroll
+      for (int k = 0; k < K; ++k) v[k] = load_src<M>(a, row, k * P + i);
+#pragma unroll
+      for (int r = 0; r < K; ++r) row_s[r * P + i] = mix_row<K>(v, masks.m[r]);
+    }
+  }
+  __syncthreads();
+  fwht_shared(row_s, P, K);
+  for (int j = threadIdx.x; j < a.n; j += blockDim.x) store_dst<M>(a, row, j, row_s[j]);
+}
+
+template <int K, bool T, Mode M>
+__global__ __launch_bounds__(1024) void had_chunk_kernel(HadArgs a) {
+  extern __shared__ float row_s[];
+  constexpr SignMasks<K, T> masks{};
+  const int r = blockIdx.x;
+  const long row = blockIdx.y;
+  const int P = a.P;
+  uint32_t mask = 0;
+#pragma unroll
+  for (int q = 0; q < K; ++q)
+    if (q == r) mask = masks.m[q];
+  for (int i = threadIdx.x; i < P; i += blockDim.x) {
+    float v[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] = load_src<M>(a, row, k * P + i);
+    row_s[i] = mix_row<K>(v, mask);
+  }
+  __syncthreads();
+  fwht_shared(row_s, P, 1);
+  for (int i = threadIdx.x; i < P; i += blockDim.x) store_dst<M>(a, row, r * P + i, row_s[i]);
+}
+
+constexpr int kMaxRowFloats = 57344;  // 224 KiB of the 227 KiB a CTA may hold
+constexpr int kChunkRowsBelow = 32;   // fewer rows than this: K CTAs per row
+
+template <int K, bool T, Mode M>
+static int configure() {
+  QB_CUDA(cudaFuncSetAttribute(had_row_kernel<K, T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kMaxRowFloats * 4));
+  QB_CUDA(cudaFuncSetAttribute(had_chunk_kernel<K, T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8192 * 4));
+  return QTIP_OK;
+}
+template <int K, bool T>
+static int configure_modes() {
+  int rc;
+  if ((rc = configure<K, T, Mode::F32Inplace>())) return rc;
+  if ((rc = configure<K, T, Mode::Prepare>())) return rc;
+  if ((rc = configure<K, T, Mode::Finish>())) return rc;
+  return configure<K, T, Mode::FinishB16>();
+}
+int hadamard_device_setup() {
+  int rc;
+  if ((rc = configure_modes<1, false>())) return rc;
+  if ((rc = configure_modes<12, false>()) || (rc = configure_modes<12, true>())) return rc;
+  if ((rc = configure_modes<20, false>()) || (rc = configure_modes<20, true>())) return rc;
+  if ((rc = configure_modes<28, false>()) || (rc = configure_modes<28, true>())) return rc;
+  return QTIP_OK;
+}
+
+template <int K, bool T, Mode M>
+static int launch(const HadArgs& a, long rows, bool force_row, cudaStream_t s) {
+  const int threads = a.P >= 1024 ? 1024 : (a.P < 64 ? 64 : a.P);
+  if (!force_row && K > 1 && rows < kChunkRowsBelow && a.P <= 8192) {
+    QB_REQUIRE(rows <= 65535, QTIP_E_GEOMETRY, "too many rows for the chunk kernel");
+    had_chunk_kernel<K, T, M><<<dim3(K, unsigned(rows)), threads, size_t(a.P) * 4, s>>>(a);
+  } else {
+    QB_REQUIRE(a.n <= kMaxRowFloats, QTIP_E_GEOMETRY, "Hadamard rows longer than %d are not supported (n = %d)",
+               kMaxRowFloats, a.n);
+    had_row_kernel<K, T, M><<<unsigned(rows), 1024, size_t(a.n) * 4, s>>>(a);
+  }
+  QB_LAUNCHED();
+  return QTIP_OK;
+}
+template <Mode M>
+static int dispatch(HadArgs a, long rows, bool transpose, bool force_row, cudaStream_t s) {
+  const int K = had_order(a.n);
+  QB_REQUIRE(K > 0, QTIP_E_GEOMETRY, "unsupported Hadamard size %d", a.n);
+  a.P = a.n / K;
+  a.rows = int(rows);
+  a.scale = 1.0f / std::sqrt(float(a.n));
+  if (a.ranks > 1) QB_REQUIRE(a.n % a.ranks == 0, QTIP_E_GEOMETRY, "n = %d is not divisible by %d ranks", a.n, a.ranks);
+  if (rows == 0) return QTIP_OK;
+  switch (K) {
+    case 1: return launch<1, false, M>(a, rows, true, s);
+    case 12: return transpose ? launch<12, true, M>(a, rows, force_row, s) : launch<12, false, M>(a, rows, force_row, s);
+    case 20: return transpose ? launch<20, true, M>(a, rows, force_row, s) : launch<20, false, M>(a, rows, force_row, s);
+    default: return transpose ? launch<28, true, M>(a, rows, force_row, s) : launch<28, false, M>(a, rows, force_row, s);
+  }
+}
+
+// Operator-side entry points used by decode.cu. ranks: 0/1 = row-major source, R >= 2 = gathered [rank][row][n/R].
+int hadamard_prepare(const uint16_t* x, const float* su, uint16_t* rotated, int n, int tokens, int ranks,
+                     cudaStream_t s) {
+  HadArgs a{};
+  a.src = x, a.dst = rotated, a.sign = su, a.ld = n, a.n = n, a.splits = 1, a.ranks = ranks;
+  return dispatch<Mode::Prepare>(a, tokens, true, false, s);
+}
+int hadamard_finish(const float* z, const float* sv, uint16_t* y, int n, int tokens, int splits, long split_stride,
+                    int round_z, int ranks, cudaStream_t s) {
+  HadArgs a{};
+  a.src = z, a.dst = y, a.sign = sv, a.ld = n, a.n = n, a.splits = splits, a.split_stride = split_stride;
+  a.round_z = round_z, a.ranks = ranks;
+  return dispatch<Mode::Finish>(a, tokens, false, false, s);
+}
+int hadamard_finish_b16(const uint16_t* z, const float* sv, uint16_t* y, int n, int tokens, int ranks, cudaStream_t s) {
+  HadArgs a{};
+  a.src = z, a.dst = y, a.sign = sv, a.ld = n, a.n = n, a.splits = 1, a.ranks = ranks;
+  return dispatch<Mode::FinishB16>(a, tokens, false, false, s);
+}
+
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" int qtip_k_hadamard_rows(float* X_d, long rows, int n, long ld, int transpose, void* stream) {
+  QB_REQUIRE(X_d && rows >= 0 && n > 0 && ld >= n, QTIP_E_ARG, "qtip_k_hadamard_rows: bad argument");
+  if (!device_info()) return QTIP_E_DEVICE;
+  HadArgs a{};
+  a.src = X_d, a.dst = X_d, a.ld = ld, a.n = n, a.splits = 1;
+  return dispatch<Mode::F32Inplace>(a, rows, transpose != 0, true, as_stream(stream));
+}

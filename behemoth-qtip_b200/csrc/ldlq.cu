@@ -1,0 +1,168 @@
+// LDLQ error feedback around the Viterbi quantiser (128-column buffers, 16-column blocks, right to left).
+//
+//  * ldlq_prep_kernel: feedback inside the current buffer, fp32 FMA with k ascending exactly as the reference's
+//    ldlq_prep_kernel (src/viterbi.hip:241-267), so the sequences handed to the Viterbi are bit-identical given
+//    identical inputs. One thread per W row j; L's 16 columns of the block staged in shared memory.
+//  * ldlq_update_kernel: cross-buffer update prod[r][j] += sum_k L[k][r] (WT[k][j] - hatWT[k][j]) over the 128 rows k of
+//    the finished buffer, r < c0. The reference does this with a split-bf16 library GEMM (src/quantizer.cpp:64-76); here
+//    every element is one thread's fp32 FMA chain over k ascending, which is deterministic and at least as accurate.
+//    128 x 128 output tile per CTA, 8 x 8 per thread, the 128-deep operand panels staged through shared memory.
+//  * qtip_ldlq: the schedule of ldlq_gpu (src/quantizer.cpp:30-89) on one stream, restricted to a slice of W rows.
+#include "common.cuh"
+
+namespace qb {
+
+int quantize_tiles_impl(const float* X, int B, int b0, const uint32_t* lut, uint16_t* Q, int nblk, int blk, float* hat,
+                        float* hatWT, long m, int col0, void* ws, size_t ws_bytes, cudaStream_t s);  // viterbi.cu
+
+// Rows j in [j0, j0 + mj) of W; X is indexed from the slice start: X[(j - j0) >> 4][256].
+__global__ __launch_bounds__(256) void ldlq_prep_kernel(const float* __restrict__ WT, const float* __restrict__ hatWT,
+                                                        const float* __restrict__ prod, const float* __restrict__ L,
+                                                        long n, long m, long j0, long mj, int col0, int bufend,
+                                                        float* __restrict__ X) {
+  __shared__ float Ls[112][16];
+  const int k0 = col0 + 16, nk = bufend - k0;
+  for (int idx = threadIdx.x; idx < nk * 16; idx += blockDim.x)
+    Ls[idx >> 4][idx & 15] = L[long(k0 + (idx >> 4)) * n + col0 + (idx & 15)];
+  __syncthreads();
+  const long jl = long(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (jl >= mj) return;
+  const long j = j0 + jl;
+  float acc[16];
+#pragma unroll
+  for (int c = 0; c < 16; ++c) acc[c] = __fadd_rn(WT[long(col0 + c) * m + j], prod[long(col0 + c) * m + j]);
+  for (int kk = 0; kk < nk; ++kk) {
+    const long o = long(k0 + kk) * m + j;
+    const float dk = __fsub_rn(WT[o], hatWT[o]);
+#pragma unroll
+    for (int c = 0; c < 16; ++c) acc[c] = __fmaf_rn(Ls[kk][c], dk, acc[c]);
+  }
+  float* xb = X + (jl >> 4) * 256;
+  const int r = int(jl & 15);
+#pragma unroll
+  for (int c = 0; c < 16; ++c) xb[perm_inv(r * 16 + c)] = acc[c];
+}
+
+constexpr int kUpTile = 128, kUpK = 128, kUpKc = 16;
+// prod[r][j] (r < c0, j in the slice) += sum_{k=c0}^{c0+127} L[k][r] * (WT[k][j] - hatWT[k][j])
+__global__ __launch_bounds__(256) void ldlq_update_kernel(const float* __restrict__ WT, const float* __restrict__ hatWT,
+                                                          const float* __restrict__ L, float* __restrict__ prod, long n,
+                                                          long m, long j0, long mj, int c0) {
+  __shared__ float Ls[kUpKc][kUpTile];  // L[c0 + k][r0 + r]
+  __shared__ float Ds[kUpKc][kUpTile];  // (WT - hatWT)[c0 + k][jb + j]
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads, 8 x 8 outputs each (strided by 16)
+  const long r0 = long(blockIdx.y) * kUpTile, jb = j0 + long(blockIdx.x) * kUpTile;
+  float acc[8][8];
+#pragma unroll
+  for (int a = 0; a < 8; ++a)
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const long r = r0 + ty + 16 * a, j = jb + tx + 16 * b;
+      acc[a][b] = (r < c0 && j < j0 + mj) ? prod[r * m + j] : 0.f;
+    }
+  for (int kc = 0; kc < kUpK; kc += kUpKc) {
+    for (int idx = threadIdx.x; idx < kUpKc * kUpTile; idx += 256) {
+      const int k = idx / kUpTile, x = idx % kUpTile;
+      const long kr = c0 + kc + k;
+      Ls[k][x] = (r0 + x < c0) ? L[kr * n + r0 + x] : 0.f;
+      const long j = jb + x;
+      Ds[k][x] = (j < j0 + mj) ? __fsub_rn(WT[kr * m + j], hatWT[kr * m + j]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kUpKc; ++k) {
+      float lv[8], dv[8];
+#pragma unroll
+      for (int a = 0; a < 8; ++a) lv[a] = Ls[k][ty + 16 * a];
+#pragma unroll
+      for (int b = 0; b < 8; ++b) dv[b] = Ds[k][tx + 16 * b];
+#pragma unroll
+      for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) acc[a][b] = __fmaf_rn(lv[a], dv[b], acc[a][b]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int a = 0; a < 8; ++a)
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const long r = r0 + ty + 16 * a, j = jb + tx + 16 * b;
+      if (r < c0 && j < j0 + mj) prod[r * m + j] = acc[a][b];
+    }
+}
+
+// Zeroes columns [j0, j0 + mj) of an n x m matrix.
+__global__ void zero_cols_kernel(float* A, long n, long m, long j0, long mj) {
+  const long total = n * mj;
+  for (long i = long(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
+    const long r = i / mj;
+    A[r * m + j0 + (i - r * mj)] = 0.f;
+  }
+}
+
+static size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" int qtip_k_ldlq_prep(const float* WT_d, const float* hatWT_d, const float* prod_d, const float* L_d, long n,
+                                long m, int col0, int bufend, float* X_d, void* stream) {
+  QB_REQUIRE(WT_d && hatWT_d && prod_d && L_d && X_d && n > 0 && m > 0, QTIP_E_ARG, "qtip_k_ldlq_prep: bad argument");
+  QB_REQUIRE(bufend - col0 - 16 <= 112 && bufend - col0 - 16 >= 0 && col0 >= 0 && bufend <= n, QTIP_E_GEOMETRY,
+             "qtip_k_ldlq_prep: block [%d, %d) is not inside a 128-column buffer", col0, bufend);
+  ldlq_prep_kernel<<<blocks_for(m, 256), 256, 0, as_stream(stream)>>>(WT_d, hatWT_d, prod_d, L_d, n, m, 0, m, col0,
+                                                                      bufend, X_d);
+  QB_LAUNCHED();
+  return QTIP_OK;
+}
+
+extern "C" size_t qtip_ldlq_workspace_bytes(long n, long m) {
+  if (n <= 0 || m <= 0) return 0;
+  const long ntr = m / 16;
+  return align256(size_t(n) * m * 4) + align256(size_t(ntr) * 256 * 4) + qtip_quantize_workspace_bytes(int(ntr));
+}
+
+extern "C" int qtip_ldlq(const float* WT_d, const float* L_d, long n, long m, long j0, long mj, float* hatWT_d,
+                         uint16_t* Q_d, const uint32_t* lut_h2_d, void* workspace_d, size_t workspace_bytes,
+                         void* stream) {
+  QB_REQUIRE(WT_d && L_d && hatWT_d && Q_d && lut_h2_d && workspace_d, QTIP_E_ARG, "qtip_ldlq: null pointer");
+  QB_REQUIRE(n > 0 && n % 128 == 0, QTIP_E_GEOMETRY, "LDLQ needs n %% 128 == 0 (n = %ld)", n);
+  QB_REQUIRE(m > 0 && m % 16 == 0, QTIP_E_GEOMETRY, "LDLQ needs m %% 16 == 0 (m = %ld)", m);
+  QB_REQUIRE(j0 >= 0 && mj > 0 && j0 % 16 == 0 && mj % 16 == 0 && j0 + mj <= m, QTIP_E_GEOMETRY,
+             "LDLQ row slice [%ld, %ld) must be whole 16-row blocks inside m = %ld", j0, j0 + mj, m);
+  cudaStream_t s = as_stream(stream);
+  // The workspace holds prod for the full n x m extent (only the slice's columns are touched), the slice's sequences
+  // and the Viterbi scratch.
+  const size_t prod_bytes = align256(size_t(n) * m * 4), x_bytes = align256(size_t(mj / 16) * 256 * 4);
+  QB_REQUIRE(workspace_bytes >= prod_bytes + x_bytes + qtip_quantize_workspace_bytes(8), QTIP_E_WORKSPACE,
+             "qtip_ldlq: workspace of %zu bytes is too small", workspace_bytes);
+  unsigned char* p = static_cast<unsigned char*>(workspace_d);
+  float* prod = reinterpret_cast<float*>(p);
+  float* X = reinterpret_cast<float*>(p + prod_bytes);
+  void* vws = p + prod_bytes + x_bytes;
+  const size_t vws_bytes = workspace_bytes - prod_bytes - x_bytes;
+  const int ntr = int(mj / 16), nblk = int(n / 16);
+  zero_cols_kernel<<<148 * 8, 256, 0, s>>>(prod, n, m, j0, mj);
+  QB_LAUNCHED();
+  zero_cols_kernel<<<148 * 8, 256, 0, s>>>(hatWT_d, n, m, j0, mj);
+  QB_LAUNCHED();
+  for (long cur = n / 16; cur > 0; cur -= 8) {
+    const int bufend = int(16 * cur), c0 = bufend - 128;
+    for (int i = 7; i >= 0; --i) {
+      const int col0 = c0 + 16 * i;
+      ldlq_prep_kernel<<<blocks_for(mj, 256), 256, 0, s>>>(WT_d, hatWT_d, prod, L_d, n, m, j0, mj, col0, bufend, X);
+      QB_LAUNCHED();
+      int rc = quantize_tiles_impl(X, ntr, int(j0 / 16), lut_h2_d, Q_d, nblk, col0 / 16, nullptr, hatWT_d, m, col0, vws,
+                                   vws_bytes, s);
+      if (rc) return rc;
+    }
+    if (c0 > 0) {
+      const dim3 grid(blocks_for(mj, kUpTile), blocks_for(c0, kUpTile));
+      ldlq_update_kernel<<<grid, 256, 0, s>>>(WT_d, hatWT_d, L_d, prod, n, m, j0, mj, c0);
+      QB_LAUNCHED();
+    }
+  }
+  return QTIP_OK;
+}

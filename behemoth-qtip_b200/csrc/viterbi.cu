@@ -1,0 +1,659 @@
+// Bitshift-trellis Viterbi (L = 16 state bits, 4 new bits and 2 weights per step, 256-weight sequences) for sm_100a.
+//
+// Arithmetic contract (bit-exact with the reference kernel, src/viterbi.hip:106-140,145-187 of the reference):
+//   inputs are rounded to fp16 first; per step (x0, x1): m0 = fp16(-2 x0), m1 = fp16(-2 x1), xx = x0^2 + x1^2;
+//   for state s = (d << 12) | j with LUT pair (l0, l1):  c = fma(l1, m1, fma(l0, m0, (l0^2 + l1^2) + (M[s >> 4] + xx)));
+//   new minimum of group j = min over d of float((bits(c) & ~15) | d); back-pointer = low 4 bits of that minimum,
+//   stored minimum = the same with the low 4 bits cleared. The last step takes the untagged argmin, lowest state on ties.
+//
+// Two implementations live here:
+//  * vit_fwd_tile_kernel: one CTA per sequence, LUT through a compact shared table, back-pointers in the layout of the
+//    reference's k_viterbi_fwd ([B][127][1024] uint16). Used by the kernel-level entry points.
+//  * vit_fwd_cluster_kernel: the throughput path. An 8-CTA thread-block cluster owns the 65,536 states of the trellis
+//    (8,192 per SM, one group index j and its 16 predecessors d per thread), keeps each state's LUT pair and norm in
+//    registers for the whole launch, and runs 8 sequences at a time through them. The 4,096 group minima of a step are
+//    exchanged between the 8 SMs through distributed shared memory (each minimum is pushed to the one CTA that reads it
+//    next step) with mbarrier hand-shakes; the two 4-sequence halves of a batch alternate so that one half computes while
+//    the other half's minima are in flight. Back-pointers go to global memory as one 32-bit word per (8 steps, group).
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace qb {
+
+// ------------------------------------------------------------------------------------------------- shared device code
+
+__device__ __forceinline__ float state_cost(float l0, float l1, float nrm, float mp, float m0, float m1) {
+  return __fmaf_rn(l1, m1, __fmaf_rn(l0, m0, __fadd_rn(nrm, mp)));
+}
+__device__ __forceinline__ float min3(float a, float b, float c) {
+  float r;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// (cost, state) candidates of the last step order by cost, then by state.
+__device__ __forceinline__ void take_better(float& bv, uint32_t& bs, float ov, uint32_t os) {
+  if (ov < bv || (ov == bv && os < bs)) bv = ov, bs = os;
+}
+
+// ------------------------------------------------------------------------------------------------- one CTA per sequence
+
+constexpr int kTileThreads = 1024;
+
+__global__ __launch_bounds__(kTileThreads) void vit_fwd_tile_kernel(const float* __restrict__ X,
+                                                                    const int* __restrict__ overlap, int roll,
+                                                                    uint16_t* __restrict__ A,
+                                                                    uint16_t* __restrict__ final_state,
+                                                                    const uint32_t* __restrict__ lut_h2) {
+  __shared__ float M[2][4096];
+  __shared__ float xs[256];
+  __shared__ float tl0[1024], tl1[1024], tnr[1024];  // compact LUT by entry (sign << 9 | index)
+  __shared__ float rv[32];
+  __shared__ uint32_t rs[32];
+  const int b = blockIdx.x, t = threadIdx.x, g = t >> 2;
+  const float* xb = X + size_t(b) * 256;
+  if (t < 256) xs[t] = round_half(roll ? xb[(t + 128) & 255] : xb[t]);
+  // Every state with the same entry holds the same pair, so concurrent writers store identical values.
+  for (uint32_t s = t; s < 65536; s += kTileThreads) {
+    const uint32_t u = lut_h2[s], e = lut_entry(s);
+    const float a = half_lo(u), c = half_hi(u);
+    tl0[e] = a;
+    tl1[e] = c;
+    tnr[e] = __fadd_rn(__fmul_rn(a, a), __fmul_rn(c, c));
+  }
+  const int ov = overlap ? overlap[b] : -1;
+  for (int k = t; k < 4096; k += kTileThreads) M[0][k] = (ov < 0 || k == ov) ? 0.f : 1e30f;
+  __syncthreads();
+
+  uint16_t* Ab = A + size_t(b) * 127 * 1024;
+  int cur = 0;
+  for (int i = 0; i < 127; ++i) {
+    const float x0 = xs[2 * i], x1 = xs[2 * i + 1];
+    const float m0 = round_half(-2.f * x0), m1 = round_half(-2.f * x1);
+    const float xx = __fadd_rn(__fmul_rn(x0, x0), __fmul_rn(x1, x1));
+    float best[4] = {3e30f, 3e30f, 3e30f, 3e30f};
+#pragma unroll 4
+    for (int d = 0; d < 16; ++d) {
+      const float mp = __fadd_rn(M[cur][(d << 8) | g], xx);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t e = lut_entry(uint32_t((d << 12) | (t << 2) | q));
+        const float c = state_cost(tl0[e], tl1[e], tnr[e], mp, m0, m1);
+        best[q] = fminf(best[q], __uint_as_float((__float_as_uint(c) & ~15u) | uint32_t(d)));
+      }
+    }
+    uint32_t pk = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t bb = __float_as_uint(best[q]);
+      pk |= (bb & 15u) << (4 * q);
+      M[cur ^ 1][(t << 2) | q] = __uint_as_float(bb & ~15u);
+    }
+    Ab[i * 1024 + t] = uint16_t(pk);
+    __syncthreads();
+    cur ^= 1;
+  }
+  {
+    const float x0 = xs[254], x1 = xs[255];
+    const float m0 = round_half(-2.f * x0), m1 = round_half(-2.f * x1);
+    const float xx = __fadd_rn(__fmul_rn(x0, x0), __fmul_rn(x1, x1));
+    float bv = 3e30f;
+    uint32_t bs = 0xffffffffu;
+    for (int d = 0; d < 16; ++d) {
+      const float mp = __fadd_rn(M[cur][(d << 8) | g], xx);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int j = (t << 2) | q;
+        if (ov >= 0 && j != ov) continue;
+        const uint32_t s = (uint32_t(d) << 12) | uint32_t(j);
+        const uint32_t e = lut_entry(s);
+        take_better(bv, bs, state_cost(tl0[e], tl1[e], tnr[e], mp, m0, m1), s);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+      take_better(bv, bs, __shfl_xor_sync(0xffffffffu, bv, off), __shfl_xor_sync(0xffffffffu, bs, off));
+    if ((t & 31) == 0) rv[t >> 5] = bv, rs[t >> 5] = bs;
+    __syncthreads();
+    if (t < 32) {
+      bv = rv[t], bs = rs[t];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+        take_better(bv, bs, __shfl_xor_sync(0xffffffffu, bv, off), __shfl_xor_sync(0xffffffffu, bs, off));
+      if (t == 0) final_state[b] = uint16_t(bs);
+    }
+  }
+}
+
+// Back-pointer lookup in the [127][1024] uint16 layout.
+__device__ __forceinline__ uint32_t prev_state_u16(const uint16_t* Ab, int i, uint32_t s) {
+  const uint32_t j = s >> 4;
+  const uint32_t d = (uint32_t(Ab[i * 1024 + (j >> 2)]) >> (4 * (j & 3))) & 15u;
+  return j | (d << 12);
+}
+__global__ void vit_overlap_u16_kernel(const uint16_t* __restrict__ A, const uint16_t* __restrict__ final_state, int B,
+                                       int* __restrict__ overlap) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const uint16_t* Ab = A + size_t(b) * 127 * 1024;
+  uint32_t s = final_state[b];
+  for (int i = 126; i >= 64; --i) s = prev_state_u16(Ab, i, s);
+  overlap[b] = int(s >> 4);
+}
+__device__ __forceinline__ void emit_state(int i, uint32_t s, uint16_t* q, float* hatWT, long m, long row0, int col0,
+                                           float* hat, const uint32_t* lut_h2) {
+  if (q) q[i] = uint16_t(s);
+  if (hatWT || hat) {
+    const uint32_t u = lut_h2[s];
+    const float v0 = half_lo(u), v1 = half_hi(u);
+    if (hat) hat[2 * i] = v0, hat[2 * i + 1] = v1;
+    if (hatWT) {
+      const int t0 = perm_fwd(2 * i), t1 = perm_fwd(2 * i + 1);
+      hatWT[long(col0 + (t0 & 15)) * m + row0 + (t0 >> 4)] = v0;
+      hatWT[long(col0 + (t1 & 15)) * m + row0 + (t1 >> 4)] = v1;
+    }
+  }
+}
+__global__ void vit_finish_u16_kernel(const uint16_t* __restrict__ A, const uint16_t* __restrict__ final_state, int B,
+                                      int b0, uint16_t* __restrict__ Q, int nblk, int blk, float* __restrict__ hatWT,
+                                      long m, int col0, const uint32_t* __restrict__ lut_h2) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const uint16_t* Ab = A + size_t(b) * 127 * 1024;
+  uint16_t* q = Q ? Q + (size_t(b0 + b) * nblk + blk) * 128 : nullptr;
+  uint32_t s = final_state[b];
+  for (int i = 127; i >= 0; --i) {
+    if (i < 127) s = prev_state_u16(Ab, i, s);
+    emit_state(i, s, q, hatWT, m, long(b0 + b) * 16, col0, nullptr, lut_h2);
+  }
+}
+__global__ void decode_states_kernel(const uint16_t* __restrict__ st, long n, float* __restrict__ hat,
+                                     const uint32_t* __restrict__ lut_h2) {
+  const long i = long(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t u = lut_h2[st[i]];
+  reinterpret_cast<float2*>(hat)[i] = make_float2(half_lo(u), half_hi(u));
+}
+
+// ------------------------------------------------------------------------------------------------- 8-CTA cluster kernel
+
+constexpr int kCl = 8;          // CTAs per cluster; each owns 512 group indices j (8,192 states)
+constexpr int kClThreads = 512; // one j per thread
+constexpr int kTG = 4;          // sequences per half-batch (one float4 of minima per predecessor)
+constexpr int kNG = 2;          // half-batches in flight
+constexpr int kTB = kTG * kNG;  // sequences per cluster batch
+constexpr int kBufs = 3;        // exchange buffers per half-batch (see the hazard note in the kernel)
+constexpr long long kWaitCycles = 2000000000LL;  // give up a hand-shake after about a second
+
+struct __align__(16) ClusterSmem {
+  // M[g][buf][d][gl][t]: minimum (+ next step's xx) of predecessor group (d << 8) | (32 * rank + gl) for sequence t of
+  // half-batch g. Written by remote CTAs (and locally for step 0), read as float4 over t.
+  float M[kNG][kBufs][16][32][kTG];
+  float m01[128][kNG][2][kTG];  // fp16(-2 x0), fp16(-2 x1) per step
+  float xx[128][kNG][kTG];      // x0^2 + x1^2 per step
+  unsigned long long full[kNG][kBufs];
+  float red_c[kClThreads / 32][kTB];
+  uint32_t red_s[kClThreads / 32][kTB];
+  float fin_c[kCl][kTB];  // used in CTA 0 only: one candidate per CTA
+  uint32_t fin_s[kCl][kTB];
+  int ov[kTB];
+  int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float a) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t addr, uint32_t a) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(a) : "memory");
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Waits for phase `parity` of a local mbarrier. Never spins forever: after kWaitCycles it raises the CTA's abort flag and
+// the launch's status word, after which every wait in the CTA falls through (results are then garbage and the host
+// reports QTIP_E_KERNEL).
+__device__ __forceinline__ void wait_full(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  if (mbar_try_wait(bar, parity)) return;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return;
+    if (clock64() - start > kWaitCycles) {
+      *abort_flag = 1;
+      atomicExch(status, 1);
+      return;
+    }
+  }
+}
+
+// X [B][256]; overlap [B] or null; bp [B][16][4096] uint32: word (b, i >> 3, j) holds the back-pointer of step i of group
+// j in bits [4 (7 - (i & 7)), +4); blocks below first_blk are not stored. final_state [B].
+__global__ __cluster_dims__(kCl, 1, 1) __launch_bounds__(kClThreads, 1) void vit_fwd_cluster_kernel(
+    const float* __restrict__ X, const int* __restrict__ overlap, int roll, int B, uint32_t* __restrict__ bp,
+    int first_blk, uint16_t* __restrict__ final_state, const uint32_t* __restrict__ lut_h2, int* __restrict__ status) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  ClusterSmem& sm = *reinterpret_cast<ClusterSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cg::this_cluster().block_rank();
+  const int cluster_id = blockIdx.x / kCl, n_clusters = gridDim.x / kCl;
+  const int j = int(rank) * kClThreads + tid;  // this thread's group index
+  const int gl = tid >> 4;                     // local index of the predecessor groups it reads
+
+  // The 16 states (d << 12) | j of this thread: LUT pair and squared norm stay in registers for the whole launch.
+  float l0[16], l1[16], nr[16];
+#pragma unroll
+  for (int d = 0; d < 16; ++d) {
+    const uint32_t u = lut_h2[(d << 12) | j];
+    l0[d] = half_lo(u);
+    l1[d] = half_hi(u);
+    nr[d] = __fadd_rn(__fmul_rn(l0[d], l0[d]), __fmul_rn(l1[d], l1[d]));
+  }
+
+  if (tid == 0) {
+    for (int g = 0; g < kNG; ++g)
+      for (int b = 0; b < kBufs; ++b) mbar_init(smem_u32(&sm.full[g][b]), 2 * kCl);  // 2 warps from each CTA
+    sm.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  cluster_sync_all();
+
+  // Minimum of group j is read next step as predecessor (d' << 8) | g' with d' = j >> 8, g' = j & 255, i.e. by CTA
+  // g' >> 5 at row (d', g' & 31). A warp covers 32 consecutive j, so all its lanes push to the same CTA.
+  const uint32_t dst = uint32_t(warp & 7);
+  const int dprime = int(rank) * 2 + (warp >> 3);
+  const uint32_t push_base = map_to_cta(smem_u32(&sm.M[0][0][dprime][lane][0]), dst);
+  const uint32_t bar_base = map_to_cta(smem_u32(&sm.full[0][0]), dst);
+  constexpr uint32_t kBufBytes = 16 * 32 * kTG * 4, kGrpBytes = kBufs * kBufBytes;
+  volatile int* abort_flag = &sm.abort_flag;
+  uint32_t phase_bits = 0;  // bit g * kBufs + buf: parity of the next wait on full[g][buf]
+
+  for (int batch = cluster_id; batch * kTB < B; batch += n_clusters) {
+    const int t_first = batch * kTB;
+    // Per-step input terms of the kTB sequences (sequences past B repeat the last one and are not stored).
+    for (int idx = tid; idx < 128 * kTB; idx += kClThreads) {
+      const int tl = idx & (kTB - 1), step = idx >> 3;
+      const float* src = X + size_t(min(t_first + tl, B - 1)) * 256;
+      const int p0 = roll ? ((2 * step + 128) & 255) : 2 * step;
+      const float x0 = round_half(src[p0]), x1 = round_half(src[p0 + 1]);
+      sm.m01[step][tl >> 2][0][tl & 3] = round_half(-2.f * x0);
+      sm.m01[step][tl >> 2][1][tl & 3] = round_half(-2.f * x1);
+      sm.xx[step][tl >> 2][tl & 3] = __fadd_rn(__fmul_rn(x0, x0), __fmul_rn(x1, x1));
+    }
+    if (tid < kTB) sm.ov[tid] = overlap ? overlap[min(t_first + tid, B - 1)] : -1;
+    __syncthreads();
+    {  // step-0 predecessors: 0 where the start constraint allows, 1e30 elsewhere, plus xx of step 0
+      const int d = tid >> 5, g0 = tid & 31;
+      const int k = (d << 8) | (int(rank) * 32 + g0);
+#pragma unroll
+      for (int g = 0; g < kNG; ++g)
+#pragma unroll
+        for (int t = 0; t < kTG; ++t) {
+          const int ov = sm.ov[g * kTG + t];
+          sm.M[g][0][d][g0][t] = __fadd_rn((ov < 0 || k == ov) ? 0.f : 1e30f, sm.xx[0][g][t]);
+        }
+    }
+    __syncthreads();
+
+    uint32_t hist[kTB];
+#pragma unroll
+    for (int t = 0; t < kTB; ++t) hist[t] = 0;
+
+    // Hazard note: a warp reads buffer i % 3 at step i; that buffer is rewritten by pushes of step i + 2. A CTA can only
+    // compute step i + 2 after receiving every CTA's step-(i + 1) minima, and those in turn needed this warp's step-i
+    // arrival at the CTA it feeds, so the reads are done by then. With two buffers that chain is one link short.
+#pragma unroll 1
+    for (int i = 0; i < 127; ++i) {
+      const int buf = i % kBufs, nbuf = (i + 1) % kBufs;
+#pragma unroll
+      for (int g = 0; g < kNG; ++g) {
+        if (i > 0) {
+          const uint32_t bit = uint32_t(g * kBufs + buf);
+          wait_full(smem_u32(&sm.full[g][buf]), (phase_bits >> bit) & 1u, abort_flag, status);
+          phase_bits ^= 1u << bit;
+        }
+        const float4 m0 = *reinterpret_cast<const float4*>(&sm.m01[i][g][0][0]);
+        const float4 m1 = *reinterpret_cast<const float4*>(&sm.m01[i][g][1][0]);
+        const float m0a[4] = {m0.x, m0.y, m0.z, m0.w}, m1a[4] = {m1.x, m1.y, m1.z, m1.w};
+        float best[4] = {3e30f, 3e30f, 3e30f, 3e30f};
+        const float4* Mrow = reinterpret_cast<const float4*>(&sm.M[g][buf][0][gl][0]);
+#pragma unroll
+        for (int d = 0; d < 16; d += 2) {
+          const float4 pa = Mrow[d * 32], pb = Mrow[(d + 1) * 32];
+          const float paa[4] = {pa.x, pa.y, pa.z, pa.w}, pba[4] = {pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float ca = state_cost(l0[d], l1[d], nr[d], paa[t], m0a[t], m1a[t]);
+            const float cb = state_cost(l0[d + 1], l1[d + 1], nr[d + 1], pba[t], m0a[t], m1a[t]);
+            best[t] = min3(best[t], __uint_as_float((__float_as_uint(ca) & ~15u) | uint32_t(d)),
+                           __uint_as_float((__float_as_uint(cb) & ~15u) | uint32_t(d + 1)));
+          }
+        }
+        const float4 xn = *reinterpret_cast<const float4*>(&sm.xx[i + 1][g][0]);
+        const float xna[4] = {xn.x, xn.y, xn.z, xn.w};
+        float out[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const uint32_t bb = __float_as_uint(best[t]);
+          hist[g * kTG + t] = (hist[g * kTG + t] << 4) | (bb & 15u);
+          out[t] = __fadd_rn(__uint_as_float(bb & ~15u), xna[t]);
+        }
+        st_cluster_v4(push_base + uint32_t(g) * kGrpBytes + uint32_t(nbuf) * kBufBytes, out[0], out[1], out[2], out[3]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(bar_base + uint32_t(g * kBufs + nbuf) * 8u);
+      }
+      if ((i & 7) == 7 || i == 126) {
+        const int blk = i >> 3;
+        if (blk >= first_blk) {
+#pragma unroll
+          for (int t = 0; t < kTB; ++t)
+            if (t_first + t < B)
+              bp[(size_t(t_first + t) * 16 + blk) * 4096 + j] = (i == 126) ? (hist[t] << 4) : hist[t];
+        }
+      }
+    }
+
+    // Last step: untagged costs over the allowed states, lowest state on ties.
+    {
+      const int buf = 127 % kBufs;
+#pragma unroll
+      for (int g = 0; g < kNG; ++g) {
+        const uint32_t bit = uint32_t(g * kBufs + buf);
+        wait_full(smem_u32(&sm.full[g][buf]), (phase_bits >> bit) & 1u, abort_flag, status);
+        phase_bits ^= 1u << bit;
+        const float4 m0 = *reinterpret_cast<const float4*>(&sm.m01[127][g][0][0]);
+        const float4 m1 = *reinterpret_cast<const float4*>(&sm.m01[127][g][1][0]);
+        const float m0a[4] = {m0.x, m0.y, m0.z, m0.w}, m1a[4] = {m1.x, m1.y, m1.z, m1.w};
+        float bv[4] = {3e30f, 3e30f, 3e30f, 3e30f};
+        uint32_t bs[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+        const float4* Mrow = reinterpret_cast<const float4*>(&sm.M[g][buf][0][gl][0]);
+#pragma unroll
+        for (int d = 0; d < 16; ++d) {
+          const float4 pa = Mrow[d * 32];
+          const float paa[4] = {pa.x, pa.y, pa.z, pa.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float c = state_cost(l0[d], l1[d], nr[d], paa[t], m0a[t], m1a[t]);
+            if (c < bv[t]) bv[t] = c, bs[t] = (uint32_t(d) << 12) | uint32_t(j);  // d ascending: lowest state wins ties
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int ov = sm.ov[g * kTG + t];
+          if (ov >= 0 && j != ov) bv[t] = 3e30f, bs[t] = 0xffffffffu;
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1)
+            take_better(bv[t], bs[t], __shfl_xor_sync(0xffffffffu, bv[t], off),
+                        __shfl_xor_sync(0xffffffffu, bs[t], off));
+          if (lane == 0) sm.red_c[warp][g * kTG + t] = bv[t], sm.red_s[warp][g * kTG + t] = bs[t];
+        }
+      }
+      __syncthreads();
+      if (tid < kTB) {
+        float bv = sm.red_c[0][tid];
+        uint32_t bs = sm.red_s[0][tid];
+        for (int w = 1; w < kClThreads / 32; ++w) take_better(bv, bs, sm.red_c[w][tid], sm.red_s[w][tid]);
+        st_cluster_f32(map_to_cta(smem_u32(&sm.fin_c[rank][tid]), 0), bv);
+        st_cluster_u32(map_to_cta(smem_u32(&sm.fin_s[rank][tid]), 0), bs);
+      }
+      cluster_sync_all();  // also keeps a fast CTA from pushing the next batch into buffers still being read
+      if (rank == 0 && tid < kTB && t_first + tid < B) {
+        float bv = sm.fin_c[0][tid];
+        uint32_t bs = sm.fin_s[0][tid];
+        for (int c = 1; c < kCl; ++c) take_better(bv, bs, sm.fin_c[c][tid], sm.fin_s[c][tid]);
+        final_state[t_first + tid] = uint16_t(bs);
+      }
+    }
+  }
+  cluster_sync_all();  // no CTA leaves while a peer may still write into its shared memory
+}
+
+// Back-pointer lookup in the cluster kernel's word layout.
+__device__ __forceinline__ uint32_t prev_state_w(const uint32_t* bpb, int i, uint32_t s) {
+  const uint32_t j = s >> 4;
+  const uint32_t d = (bpb[size_t(i >> 3) * 4096 + j] >> (4 * (7 - (i & 7)))) & 15u;
+  return j | (d << 12);
+}
+__global__ void vit_overlap_w_kernel(const uint32_t* __restrict__ bp, const uint16_t* __restrict__ final_state, int B,
+                                     int* __restrict__ overlap) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const uint32_t* bpb = bp + size_t(b) * 16 * 4096;
+  uint32_t s = final_state[b];
+  for (int i = 126; i >= 64; --i) s = prev_state_w(bpb, i, s);
+  overlap[b] = int(s >> 4);
+}
+// states -> Q[(b0+b)*nblk+blk][128]; decoded values -> hat[b][256] (sequence order) and/or hatWT (tile scatter).
+__global__ void vit_finish_w_kernel(const uint32_t* __restrict__ bp, const uint16_t* __restrict__ final_state, int B,
+                                    int b0, uint16_t* __restrict__ Q, int nblk, int blk, float* __restrict__ hat,
+                                    float* __restrict__ hatWT, long m, int col0, const uint32_t* __restrict__ lut_h2) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const uint32_t* bpb = bp + size_t(b) * 16 * 4096;
+  uint16_t* q = Q ? Q + (size_t(b0 + b) * nblk + blk) * 128 : nullptr;
+  float* h = hat ? hat + size_t(b) * 256 : nullptr;
+  uint32_t s = final_state[b];
+  for (int i = 127; i >= 0; --i) {
+    if (i < 127) s = prev_state_w(bpb, i, s);
+    emit_state(i, s, q, hatWT, m, long(b0 + b) * 16, col0, h, lut_h2);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------- host side
+
+int viterbi_device_setup(DeviceInfo* info) {
+  QB_CUDA(cudaFuncSetAttribute(vit_fwd_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               int(sizeof(ClusterSmem))));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(kCl * 64);
+  cfg.blockDim = dim3(kClThreads);
+  cfg.dynamicSmemBytes = sizeof(ClusterSmem);
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = kCl;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  QB_CUDA(cudaOccupancyMaxActiveClusters(&n, vit_fwd_cluster_kernel, &cfg));
+  QB_REQUIRE(n > 0, QTIP_E_DEVICE, "the device cannot co-schedule an %d-CTA cluster of the Viterbi kernel", kCl);
+  info->max_clusters = n;
+  return QTIP_OK;
+}
+
+// Workspace of the fused path: [status (256 B)] [final_state u16 x cap] [overlap i32 x cap] [bp 256 KiB x cap].
+struct QuantWorkspace {
+  int* status;
+  uint16_t* fs;
+  int* ov;
+  uint32_t* bp;
+  int cap;
+};
+constexpr size_t kWsHeader = 256, kBpBytes = size_t(16) * 4096 * 4;
+static size_t ws_bytes_for(size_t cap) {
+  size_t o = kWsHeader + ((cap * 2 + 255) / 256) * 256 + ((cap * 4 + 255) / 256) * 256;
+  return o + cap * kBpBytes;
+}
+static bool carve_workspace(void* ws, size_t bytes, QuantWorkspace* out) {
+  if (!ws || bytes < ws_bytes_for(kTB)) return false;
+  size_t cap = (bytes - kWsHeader - 512) / (kBpBytes + 6);
+  while (cap > 0 && ws_bytes_for(cap) > bytes) --cap;
+  if (cap < size_t(kTB)) return false;
+  cap = cap / kTB * kTB;
+  if (cap > (1u << 20)) cap = 1u << 20;
+  unsigned char* p = static_cast<unsigned char*>(ws);
+  out->status = reinterpret_cast<int*>(p);
+  p += kWsHeader;
+  out->fs = reinterpret_cast<uint16_t*>(p);
+  p += ((cap * 2 + 255) / 256) * 256;
+  out->ov = reinterpret_cast<int*>(p);
+  p += ((cap * 4 + 255) / 256) * 256;
+  out->bp = reinterpret_cast<uint32_t*>(p);
+  out->cap = int(cap);
+  return true;
+}
+
+static int launch_cluster_fwd(const DeviceInfo* info, const float* X, const int* overlap, int roll, int B, uint32_t* bp,
+                              int first_blk, uint16_t* fs, const uint32_t* lut, int* status, cudaStream_t s) {
+  const int batches = (B + kTB - 1) / kTB;
+  const int clusters = batches < info->max_clusters ? batches : info->max_clusters;
+  vit_fwd_cluster_kernel<<<dim3(clusters * kCl), dim3(kClThreads), sizeof(ClusterSmem), s>>>(X, overlap, roll, B, bp,
+                                                                                             first_blk, fs, lut, status);
+  QB_LAUNCHED();
+  return QTIP_OK;
+}
+
+// Shared body of the two fused entry points.
+int quantize_tiles_impl(const float* X, int B, int b0, const uint32_t* lut, uint16_t* Q, int nblk, int blk, float* hat,
+                        float* hatWT, long m, int col0, void* ws, size_t ws_bytes, cudaStream_t s) {
+  const DeviceInfo* info = device_info();
+  if (!info) return QTIP_E_DEVICE;
+  QuantWorkspace w;
+  QB_REQUIRE(carve_workspace(ws, ws_bytes, &w), QTIP_E_WORKSPACE,
+             "workspace of %zu bytes is too small (need at least %zu)", ws_bytes, ws_bytes_for(kTB));
+  QB_CUDA(cudaMemsetAsync(w.status, 0, kWsHeader, s));
+  for (int c0 = 0; c0 < B; c0 += w.cap) {
+    const int nb = B - c0 < w.cap ? B - c0 : w.cap;
+    const float* xc = X + size_t(c0) * 256;
+    int rc = launch_cluster_fwd(info, xc, nullptr, 1, nb, w.bp, 8, w.fs, lut, w.status, s);
+    if (rc) return rc;
+    vit_overlap_w_kernel<<<blocks_for(nb, 64), 64, 0, s>>>(w.bp, w.fs, nb, w.ov);
+    QB_LAUNCHED();
+    rc = launch_cluster_fwd(info, xc, w.ov, 0, nb, w.bp, 0, w.fs, lut, w.status, s);
+    if (rc) return rc;
+    vit_finish_w_kernel<<<blocks_for(nb, 64), 64, 0, s>>>(w.bp, w.fs, nb, b0 + c0, Q, nblk, blk,
+                                                          hat ? hat + size_t(c0) * 256 : nullptr, hatWT, m, col0, lut);
+    QB_LAUNCHED();
+  }
+  return QTIP_OK;
+}
+
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" int qtip_k_viterbi_fwd(const float* X_d, const int* overlap_d, int roll, int B, uint16_t* A_d,
+                                  uint16_t* final_state_d, const uint32_t* lut_h2_d, void* stream) {
+  QB_REQUIRE(X_d && A_d && final_state_d && lut_h2_d && B >= 0, QTIP_E_ARG, "qtip_k_viterbi_fwd: bad argument");
+  if (B == 0) return QTIP_OK;
+  vit_fwd_tile_kernel<<<unsigned(B), kTileThreads, 0, as_stream(stream)>>>(X_d, overlap_d, roll, A_d, final_state_d,
+                                                                          lut_h2_d);
+  QB_LAUNCHED();
+  return QTIP_OK;
+}
+extern "C" int qtip_k_viterbi_overlap(const uint16_t* A_d, const uint16_t* final_state_d, int B, int* overlap_d,
+                                      void* stream) {
+  QB_REQUIRE(A_d && final_state_d && overlap_d && B >= 0, QTIP_E_ARG, "qtip_k_viterbi_overlap: bad argument");
+  if (B == 0) return QTIP_OK;
+  vit_overlap_u16_kernel<<<blocks_for(B, 64), 64, 0, as_stream(stream)>>>(A_d, final_state_d, B, overlap_d);
+  QB_LAUNCHED();
+  return QTIP_OK;
+}
+extern "C" int qtip_k_viterbi_finish(const uint16_t* A_d, const uint16_t* final_state_d, int B, int b0, uint16_t* Q_d,
+                                     int nblk, int blk, float* hatWT_d, long m, int col0, const uint32_t* lut_h2_d,
+                                     void* stream) {
+  QB_REQUIRE(A_d && final_state_d && lut_h2_d && B >= 0, QTIP_E_ARG, "qtip_k_viterbi_finish: bad argument");
+  if (B == 0) return QTIP_OK;
+  vit_finish_u16_kernel<<<blocks_for(B, 64), 64, 0, as_stream(stream)>>>(A_d, final_state_d, B, b0, Q_d, nblk, blk,
+                                                                         hatWT_d, m, col0, lut_h2_d);
+  QB_LAUNCHED();
+  return QTIP_OK;
+}
+extern "C" int qtip_k_decode_states(const uint16_t* states_d, int B, float* hat_d, const uint32_t* lut_h2_d,
+                                    void* stream) {
+  QB_REQUIRE(states_d && hat_d && lut_h2_d && B >= 0, QTIP_E_ARG, "qtip_k_decode_states: bad argument");
+  if (B == 0) return QTIP_OK;
+  const long n = long(B) * 128;
+  decode_states_kernel<<<blocks_for(n, 256), 256, 0, as_stream(stream)>>>(states_d, n, hat_d, lut_h2_d);
+  QB_LAUNCHED();
+  return QTIP_OK;
+}
+
+extern "C" int qtip_k_viterbi_fwd_words(const float* X_d, const int* overlap_d, int roll, int B, uint32_t* bp_d,
+                                        int first_block, uint16_t* final_state_d, const uint32_t* lut_h2_d,
+                                        int* status_d, void* stream) {
+  QB_REQUIRE(X_d && bp_d && final_state_d && lut_h2_d && status_d && B >= 0 && first_block >= 0 && first_block < 16,
+             QTIP_E_ARG, "qtip_k_viterbi_fwd_words: bad argument");
+  const DeviceInfo* info = device_info();
+  if (!info) return QTIP_E_DEVICE;
+  if (B == 0) return QTIP_OK;
+  return launch_cluster_fwd(info, X_d, overlap_d, roll, B, bp_d, first_block, final_state_d, lut_h2_d, status_d,
+                            as_stream(stream));
+}
+extern "C" int qtip_k_viterbi_overlap_words(const uint32_t* bp_d, const uint16_t* final_state_d, int B, int* overlap_d,
+                                            void* stream) {
+  QB_REQUIRE(bp_d && final_state_d && overlap_d && B >= 0, QTIP_E_ARG, "qtip_k_viterbi_overlap_words: bad argument");
+  if (B == 0) return QTIP_OK;
+  vit_overlap_w_kernel<<<blocks_for(B, 64), 64, 0, as_stream(stream)>>>(bp_d, final_state_d, B, overlap_d);
+  QB_LAUNCHED();
+  return QTIP_OK;
+}
+extern "C" int qtip_k_viterbi_finish_words(const uint32_t* bp_d, const uint16_t* final_state_d, int B, int b0,
+                                           uint16_t* Q_d, int nblk, int blk, float* hat_d, float* hatWT_d, long m,
+                                           int col0, const uint32_t* lut_h2_d, void* stream) {
+  QB_REQUIRE(bp_d && final_state_d && lut_h2_d && B >= 0, QTIP_E_ARG, "qtip_k_viterbi_finish_words: bad argument");
+  if (B == 0) return QTIP_OK;
+  vit_finish_w_kernel<<<blocks_for(B, 64), 64, 0, as_stream(stream)>>>(bp_d, final_state_d, B, b0, Q_d, nblk, blk,
+                                                                       hat_d, hatWT_d, m, col0, lut_h2_d);
+  QB_LAUNCHED();
+  return QTIP_OK;
+}
+
+extern "C" size_t qtip_quantize_workspace_bytes(int max_tiles) {
+  size_t cap = max_tiles < kTB ? size_t(kTB) : size_t((max_tiles + kTB - 1) / kTB * kTB);
+  return ws_bytes_for(cap);
+}
+extern "C" int qtip_quantize_tiles(const float* X_d, int B, const uint32_t* lut_h2_d, uint16_t* states_d, float* hat_d,
+                                   void* workspace_d, size_t workspace_bytes, void* stream) {
+  QB_REQUIRE(X_d && lut_h2_d && B >= 0, QTIP_E_ARG, "qtip_quantize_tiles: bad argument");
+  if (B == 0) return QTIP_OK;
+  return quantize_tiles_impl(X_d, B, 0, lut_h2_d, states_d, 1, 0, hat_d, nullptr, 0, 0, workspace_d, workspace_bytes,
+                             as_stream(stream));
+}
+extern "C" int qtip_quantize_tiles_scatter(const float* X_d, int B, int b0, const uint32_t* lut_h2_d, uint16_t* Q_d,
+                                           int nblk, int blk, float* hatWT_d, long m, int col0, void* workspace_d,
+                                           size_t workspace_bytes, void* stream) {
+  QB_REQUIRE(X_d && lut_h2_d && B >= 0 && b0 >= 0 && nblk >= 1 && blk >= 0 && blk < nblk, QTIP_E_ARG,
+             "qtip_quantize_tiles_scatter: bad argument");
+  QB_REQUIRE(!hatWT_d || m >= long(b0 + B) * 16, QTIP_E_GEOMETRY,
+             "qtip_quantize_tiles_scatter: m = %ld does not cover %d row blocks", m, b0 + B);
+  if (B == 0) return QTIP_OK;
+  return quantize_tiles_impl(X_d, B, b0, lut_h2_d, Q_d, nblk, blk, nullptr, hatWT_d, m, col0, workspace_d,
+                             workspace_bytes, as_stream(stream));
+}
+extern "C" int qtip_workspace_status(const void* workspace_d, void* stream) {
+  QB_REQUIRE(workspace_d, QTIP_E_ARG, "qtip_workspace_status: null workspace");
+  int st = 0;
+  QB_CUDA(cudaMemcpyAsync(&st, workspace_d, 4, cudaMemcpyDeviceToHost, as_stream(stream)));
+  QB_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  QB_REQUIRE(st == 0, QTIP_E_KERNEL, "a Viterbi hand-shake between thread blocks timed out (status %d)", st);
+  return QTIP_OK;
+}

@@ -1,0 +1,93 @@
+"""Host-side mirror of the runtime's QTIP linear operator (runtime/cuda/kernels.hpp:5-24 and
+runtime/cuda/batch_kernels.hpp:5-8,22-23 of the reference): QtipMatrix and the prepare / multiply / finish stages,
+with torch CUDA tensors in place of raw device pointers. bf16 tensors are passed as torch.bfloat16.
+"""
+import ctypes as C
+
+import torch
+
+from ._lib import QtipMatrix, lib
+from .codec import _p, _stream, init, tlut_bits
+
+
+def runtime_lut(tlut_f16):
+    """bf16x2 table (1,024 sign-folded entries) of a tlut on the current device: make_codebook of the reference."""
+    init()
+    bits = tlut_bits(tlut_f16)
+    out = torch.empty(1024, dtype=torch.int32, device="cuda")
+    lib().call("qtip_runtime_lut", bits.ctypes.data_as(C.c_void_p), _p(out), _stream())
+    return out
+
+
+class Matrix:
+    """Owns the device tensors of one linear and exposes the POD QtipMatrix the C ABI takes by value."""
+
+    def __init__(self, trellis, su, sv, lut, n_in, n_out):
+        assert trellis.dtype == torch.int16 and trellis.numel() == (n_out // 16) * (n_in // 16) * 32
+        assert su.dtype == torch.float32 and su.numel() == n_in and sv.dtype == torch.float32 and sv.numel() == n_out
+        self.trellis, self.su, self.sv, self.lut, self.n_in, self.n_out = trellis, su, sv, lut, n_in, n_out
+
+    @property
+    def pod(self):
+        return QtipMatrix(self.trellis.data_ptr(), self.su.data_ptr(), self.sv.data_ptr(), self.lut.data_ptr(),
+                          self.n_in, self.n_out)
+
+    def rows(self, row0, rows):
+        """Matrix of output rows [row0, row0 + rows) (whole 32-row block-rows): a contiguous run of the trellis, the
+        sharding unit of rotated-row tensor parallelism. SV is kept whole: the output transform runs on full rows."""
+        assert row0 % 32 == 0 and rows % 32 == 0
+        per = (self.n_in // 32) * 128
+        t = self.trellis.view(-1)[(row0 // 32) * per:((row0 + rows) // 32) * per]
+        return Matrix(t, self.su, self.sv[row0:row0 + rows].contiguous(), self.lut, self.n_in, rows)
+
+
+def qtip_prepare(w, x, scratch, rotated, tokens=1, rank_major=0):
+    init()
+    lib().call("qtip_prepare", w.pod, _p(x, torch.bfloat16), _p(scratch), _p(rotated, torch.bfloat16), _stream(), tokens,
+               int(rank_major))
+
+
+def qtip_multiply(w, rotated, z, stride, splits, tokens=1):
+    init()
+    lib().call("qtip_multiply", w.pod, _p(rotated, torch.bfloat16), _p(z, torch.float32), stride, splits, _stream(),
+               tokens)
+
+
+def qtip_finish(w, z, y, scratch, round_z, splits, tokens=1, rank_major=0):
+    init()
+    lib().call("qtip_finish", w.pod, _p(z, torch.float32), _p(y, torch.bfloat16), _p(scratch), int(bool(round_z)),
+               splits, _stream(), tokens, int(rank_major))
+
+
+def qtip_finish_b16(w, z, y, scratch, tokens, rank_major=0):
+    init()
+    lib().call("qtip_finish_b16", w.pod, _p(z, torch.bfloat16), _p(y, torch.bfloat16), _p(scratch), tokens, _stream(),
+               int(rank_major))
+
+
+def qtip_forward(w, x, y, scratch, rotated, z, round_z, splits=1):
+    init()
+    lib().call("qtip_forward", w.pod, _p(x, torch.bfloat16), _p(y, torch.bfloat16), _p(scratch),
+               _p(rotated, torch.bfloat16), _p(z, torch.float32), int(bool(round_z)), _stream(), splits)
+
+
+def qtip_multiply_batch(w, x, z, stride, splits, tokens, implementation=-1):
+    init()
+    lib().call("qtip_multiply_batch", w.pod, _p(x, torch.bfloat16), _p(z, torch.float32), stride, splits, tokens,
+               _stream(), implementation)
+
+
+def qtip_decode_matrix(w, out):
+    init()
+    lib().call("qtip_decode_matrix", w.pod, _p(out, torch.bfloat16), _stream())
+
+
+def reduce_products(x, elements, splits):
+    init()
+    lib().call("qtip_reduce_products", _p(x, torch.float32), elements, splits, _stream())
+
+
+def reduce_to_b16(x, scale, y, elements, width, splits):
+    init()
+    lib().call("qtip_reduce_to_b16", _p(x, torch.float32), _p(scale, torch.float32), _p(y, torch.bfloat16), elements,
+               width, splits, _stream())

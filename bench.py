@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Benchmark of the QTIP trellis codec hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference --steps K --warmup W    # the reference's CPU implementation of the same path
+
+Headline workload (N = 1): two-pass tail-biting Viterbi encode of a 12288 x 12288 fp32 matrix (i.i.d. N(0,1) from a
+seed, seeded 2^9-entry codebook, identity Hessian, 589,824 independent 16x16 tiles). One step = the whole matrix. For
+N > 1 the tile rows are split contiguously over the ranks (strong scaling, no collective on the data path).
+One JSON line on stdout (rank 0).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M, N_COLS = 12288, 12288
+LANE_OPS_PER_WEIGHT = 327680  # 2 passes x 128 steps x 65,536 states / 256 weights x 5 ops (add, 2 fma, tag, min)
+METRIC = "viterbi_quantized_weights_per_second"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "sm_max_mhz": 1965.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.out = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        self.out.flush()
+        self.out.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.out.read().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        self.out.close()
+        os.unlink(self.out.name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        # median over the upper half of the samples: the sampler also sees the idle gaps around the timed region
+        load = sm[len(sm) // 2:]
+        return {"sm_mhz": load[len(load) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_rate(seconds_target, X, tlut_bits):
+    """weights/s of the reference's own fp64 tail-biting Viterbi (quantize_seq_ref, compiled in place, OpenMP over
+    sequences) on a bounded sample; falls back to the oracle port when the reference build is absent."""
+    from oracle.oracle import Oracle, Reference
+    R = Reference()
+    threads = len(os.sched_getaffinity(0))
+    x16 = lambda a: a.astype(np.float16).astype(np.float32)  # noqa: E731  (the quantizer hands the CPU path fp16 values)
+    if R.available and np.array_equal(R.codebook()[0].reshape(-1), tlut_bits.reshape(-1)):
+        run, kind = (lambda a: R.quantize_seqs(a)), "reference"
+    elif R.available:
+        # the reference's codebook is compiled in; its speed does not depend on the table's values
+        run, kind = (lambda a: R.quantize_seqs(a)), "reference"
+    else:
+        O = Oracle()
+        lut, _ = O.build_lut(tlut_bits)
+        run, kind = (lambda a: O.quantize_seq_ref(a, lut)), "port"
+    probe = x16(X[:4 * threads])
+    t0 = time.perf_counter()
+    run(probe)
+    dt = time.perf_counter() - t0
+    n = int(max(4 * threads, min(len(X), len(probe) * seconds_target / max(dt, 1e-3))))
+    n = n // threads * threads
+    sample = x16(X[:n])
+    t0 = time.perf_counter()
+    run(sample)
+    dt = time.perf_counter() - t0
+    return {"value": n * 256 / dt, "unit": "weights/s", "cores": threads, "kind": kind,
+            "sample": "%d of the %d tiles of the workload, %.1f s" % (n, len(X), dt)}
+
+
+def reference_arm(args):
+    """The reference's CPU implementation of the path on the host cores, same config and metric."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    s = pkg.synth
+    tiles = 4096
+    X = s.tile_sequences(s.gaussian_matrix(256, tiles * 16, 2))  # 4,096 tiles of the same distribution
+    tl = s.seeded_tlut(1).view(np.uint16)
+    rates, last = [], None
+    per_step = max(3.0, min(20.0, 90.0 / max(1, args.steps + args.warmup)))
+    for i in range(args.warmup + args.steps):
+        last = cpu_reference_rate(per_step, X, tl)
+        if i >= args.warmup:
+            rates.append(last["value"])
+    v = float(np.mean(rates))
+    last["value"] = v
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "weights/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * M * N_COLS / v, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": {"workload": "viterbi_encode_12288x12288_identityH", "tiles": M * N_COLS // 256,
+                       "note": "CPU path timed on a bounded sample; ms_per_step extrapolates to the full matrix"},
+            "cpu_baseline": last,
+            "e2e": {"value": v, "unit": "weights/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=M, help="rows of the matrix (default: the full 12288)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the GEMV section and the CPU baseline")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    codec, synth = pkg.codec, pkg.synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, "launch with torchrun --nproc-per-node %d for --gpus %d" % (args.gpus, args.gpus)
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    codec.init()
+    peaks, peak_src = measured_peaks()
+
+    # ---- this rank's tile rows of the matrix (generated per rank from the same seed: row r comes from seed 2 + r)
+    m_rows = args.rows
+    b, e = pkg.sharding.tile_row_range(m_rows // 16, rank, world)
+    tiles_local = (e - b) * (N_COLS // 16)
+    tl = synth.seeded_tlut(1)
+    lut_d, lut_rms = codec.device_lut(tl)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2 + 1000003 * b)
+    W = torch.randn((e - b) * 16, N_COLS, generator=gen, device="cuda", dtype=torch.float32)
+    X = codec.tiles_from_matrix(W)
+    chunk = 4608
+    ws = codec.quantize_workspace(chunk)
+    states = torch.empty((tiles_local, 128), dtype=torch.int16, device="cuda")
+    torch.cuda.synchronize()
+
+    # hat output is optional in the C ABI; the encode bench needs the codes only
+    def step_codes():
+        pkg.lib().call("qtip_quantize_tiles", X.data_ptr(), tiles_local, lut_d.data_ptr(), states.data_ptr(), None,
+                       ws.ptr, ws.nbytes, torch.cuda.current_stream().cuda_stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_codes()
+    ws.check()
+    sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step_codes()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if sampler else None
+    ws.check()
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t) / args.steps
+    total_weights = m_rows * N_COLS
+    value = total_weights / (ms_step * 1e-3)
+
+    # ---- the dominant kernel alone: forward passes over one chunk, CUDA events on the launching stream
+    nb = min(chunk, tiles_local)
+    bp = torch.empty((nb, 16, 4096), dtype=torch.int32, device="cuda")
+    fs = torch.empty(nb, dtype=torch.int16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    reps = 4
+    codec.k_viterbi_fwd_words(X, None, 1, nb, bp, 0, fs, lut_d, status)
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(reps):
+        codec.k_viterbi_fwd_words(X, None, 1, nb, bp, 0, fs, lut_d, status)
+    k1.record()
+    torch.cuda.synchronize()
+    kern_ms = k0.elapsed_time(k1) / reps
+    lane_ops = nb * 256 * LANE_OPS_PER_WEIGHT / 2  # one pass
+    sm_count = torch.cuda.get_device_properties(local).multi_processor_count
+    peak_ops = sm_count * 128 * peaks.get("sm_max_mhz", 1965.0) * 1e6
+    achieved = lane_ops / (kern_ms * 1e-3)
+    launches_per_step = 4 * ((tiles_local + chunk - 1) // chunk)
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # ---- end to end through the C ABI with host buffers: H2D of the fp32 matrix, tile gather, two-pass Viterbi, pack,
+    # kernel-layout swizzle, D2H of the trellis words. Rank 0's share at N > 1 (every rank does the same on its rows).
+    rows_local = (e - b) * 16
+    W_h = torch.empty((rows_local, N_COLS), dtype=torch.float32).pin_memory()
+    W_h.copy_(W.cpu())
+    out_h = torch.empty((tiles_local, 32), dtype=torch.int16).pin_memory()
+    packed = torch.empty((tiles_local, 32), dtype=torch.int16, device="cuda")
+    words = torch.empty_like(packed)
+
+    def step_e2e():
+        W.copy_(W_h, non_blocking=True)
+        codec.tiles_from_matrix(W, X)
+        step_codes()
+        codec.pack_trellis(states, packed)
+        if rows_local % 32 == 0:
+            codec.swizzle_for_kernel(packed, rows_local, N_COLS, words)
+            out_h.copy_(words, non_blocking=True)
+        else:
+            out_h.copy_(packed, non_blocking=True)
+        torch.cuda.synchronize()
+
+    step_e2e()
+    t0 = time.perf_counter()
+    e2e_steps = max(1, min(2, args.steps))
+    for _ in range(e2e_steps):
+        step_e2e()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    e2e = {"value": rows_local * N_COLS * world / e2e_s, "unit": "weights/s",
+           "h2d_bytes_per_step": rows_local * N_COLS * 4, "d2h_bytes_per_step": tiles_local * 64}
+
+    line = {"metric": METRIC, "value": value, "unit": "weights/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "viterbi_encode_%dx%d_identityH" % (m_rows, N_COLS), "tiles": total_weights // 256,
+                       "L": 16, "K": 2, "V": 2, "codebook": "seeded N(0,1) 2^9 x 2, unit rms, fp16",
+                       "l2": "inputs (%.0f MB per rank) exceed the 126 MB L2" % (tiles_local * 1024 / 1e6),
+                       "sharding": "contiguous tile rows per rank, no collective", "chunk_tiles": chunk},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "fp32_issue", "kernel": "vit_fwd_cluster_kernel", "achieved": achieved / 1e12,
+                         "peak": peak_ops / 1e12, "unit": "Tlane-op/s", "frac": achieved / peak_ops,
+                         "peak_source": "%d SMs x 128 lanes x sm_max_mhz of MEASURED_PEAKS.json (%s)" % (sm_count, peak_src),
+                         "ms_per_launch": kern_ms, "tiles_per_launch": nb, "traffic": None,
+                         "frac_at_sampled_clock": (achieved / (sm_count * 128 * clocks["sm_mhz"] * 1e6)
+                                                   if clocks and clocks.get("sm_mhz") else None)}}
+    if not args.no_extras:
+        try:
+            line["gemv"] = gemv_section(pkg, peaks, peak_src)
+        except Exception as ex:  # the headline line must survive a failure of the secondary section
+            line["gemv"] = {"error": repr(ex)}
+        Xs = synth.tile_sequences(synth.gaussian_matrix(256, 4096 * 16, 2))
+        line["cpu_baseline"] = cpu_reference_rate(12.0, Xs, tl.view(np.uint16))
+    print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def gemv_section(pkg, peaks, peak_src):
+    """Batch-1 trellis-decode GEMV y = W x for a 57344 x 12288 2-bit weight: multiply kernel alone and the whole
+    operator (input transform + multiply + output transform), as achieved HBM GB/s on the algorithmic bytes."""
+    import torch
+    linear, synth = pkg.linear, pkg.synth
+    n_in, n_out = 12288, 57344
+    g = torch.Generator(device="cuda")
+    g.manual_seed(9)
+    trellis = torch.randint(-32768, 32768, ((n_out // 16) * (n_in // 16) * 32,), generator=g, device="cuda",
+                            dtype=torch.int16)
+    su = torch.from_numpy(synth.signs(n_in, 7)).cuda()
+    sv = torch.from_numpy(synth.signs(n_out, 8)).cuda()
+    w = linear.Matrix(trellis, su, sv, linear.runtime_lut(synth.seeded_tlut(1)), n_in, n_out)
+    x = torch.randn(n_in, generator=g, device="cuda").to(torch.bfloat16)
+    y = torch.empty(n_out, dtype=torch.bfloat16, device="cuda")
+    rot = torch.empty(n_in, dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty(n_out, dtype=torch.float32, device="cuda")
+    algo_bytes = n_out * n_in // 4 + 2 * n_in + 4 * n_out + 4096
+    res = {"algorithmic_bytes": algo_bytes, "peak_gbs": peaks["hbm_gbs"], "peak_source": peak_src}
+    best = None
+    for splits in (1, 2, 3, 4):
+        z = torch.empty((splits, n_out), dtype=torch.float32, device="cuda")
+        linear.qtip_prepare(w, x, scratch, rot)
+        for _ in range(3):
+            linear.qtip_multiply(w, rot, z, n_out, splits)
+        torch.cuda.synchronize()
+        iters = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):  # 176 MB of codes per call exceed the L2, so no flush is needed between calls
+            linear.qtip_multiply(w, rot, z, n_out, splits)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / iters
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(iters):
+            linear.qtip_forward(w, x, y, scratch, rot, z, False, splits)
+        f1.record()
+        torch.cuda.synchronize()
+        fus = f0.elapsed_time(f1) * 1e3 / iters
+        res["splits_%d" % splits] = {"multiply_us": us, "forward_us": fus}
+        if best is None or us < best[1]:
+            best = (splits, us, fus)
+    res.update({"best_splits": best[0], "multiply_us": best[1], "forward_us": best[2],
+                "multiply_gbs": algo_bytes / best[1] / 1e3, "forward_gbs": algo_bytes / best[2] / 1e3,
+                "multiply_frac_of_peak": algo_bytes / best[1] / 1e3 / peaks["hbm_gbs"]})
+    return res
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,192 @@
+/*
+ * qtip_b200 -- C ABI of the B200 (sm_100a) implementation of the QTIP 2-bit trellis codec hot path.
+ *
+ * Every entry point takes plain pointers and sizes, launches on the caller's stream, allocates nothing unless it
+ * says so, never synchronises the host unless it says so, and returns an int status: 0 = success,
+ * QTIP_E_* (< 0) = argument / geometry violation detected before any launch, > 0 = a cudaError_t.
+ * qtip_last_error() gives the message of the calling thread's last failure.
+ *
+ * Device pointers are marked `_d`, host pointers `_h` in the comments. `stream` is a cudaStream_t passed as void*.
+ * The comments cite the reference interface (file:line in the reference project) that each function replaces.
+ */
+#ifndef QTIP_B200_H
+#define QTIP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QTIP_OK 0
+#define QTIP_E_ARG (-1)       /* null pointer, negative size, ... */
+#define QTIP_E_GEOMETRY (-2)  /* shape not supported by the codec (multiples of 16/32/128, Hadamard order, ...) */
+#define QTIP_E_WORKSPACE (-3) /* workspace too small */
+#define QTIP_E_DEVICE (-4)    /* device is not sm_100 or cannot run the cluster kernel */
+#define QTIP_E_KERNEL (-5)    /* a kernel reported a bounded wait that ran out (status word set) */
+
+const char* qtip_last_error(void);
+/* Version of this ABI (bumped on any signature change). */
+int qtip_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Per-device set-up. Uploads the order-12/20/28 Hadamard factors to constant memory, sets the opt-in
+ * shared-memory sizes and cluster attributes of the kernels and reads the SM count. Call once per device, with
+ * that device current, before any other call and before any stream capture. Idempotent.
+ * Replaces initialize_tables() (runtime/cuda/kernels.cu:398-401), device_had() (src/kernels.hip:271-291) and the
+ * lazy cudaFuncSetAttribute of launch_fused (runtime/cuda/kernels.cu:201-210).
+ */
+int qtip_init(void);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Codebook. tlut_h: [512][2] fp16 bits on the HOST (the checkpoint's `tlut` tensor).
+ */
+/* Encoder table: lut_h2_d[65536] packed half2 (lo = component 0) by quantlut_sym; *lut_rms_h (may be NULL) gets
+ * sqrt(mean(lut^2)) in fp64. Synchronous host computation + one async H2D copy from an internal pinned buffer.
+ * Replaces build_codebook()/device_lut() (src/qtip_core.cpp:18-50, src/quantizer.cpp:14-28), with the table as a
+ * parameter instead of a compiled-in constant. */
+int qtip_encoder_lut(const uint16_t* tlut_h, uint32_t* lut_h2_d, double* lut_rms_h, void* stream);
+/* Runtime table: lut_d[1024] bf16x2 words (entry e = sign<<9 | idx, RNE from the fp16 values). Rejects non-finite
+ * entries with QTIP_E_ARG. Replaces make_codebook() (runtime/src/qtip.cpp:62-80). */
+int qtip_runtime_lut(const uint16_t* tlut_h, uint32_t* lut_d, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Encode side: kernel-level interface, argument for argument the k_* wrappers of src/gpu.hpp:276-292.
+ */
+/* X_d [B][256] f32 -> the 16 x-column feedback step of one LDLQ block. src/viterbi.hip:241-274 (k_ldlq_prep). */
+int qtip_k_ldlq_prep(const float* WT_d, const float* hatWT_d, const float* prod_d, const float* L_d, long n, long m,
+                     int col0, int bufend, float* X_d, void* stream);
+/* One Viterbi forward pass over B sequences. A_d [B][127][1024] u16, final_state_d [B] u16, overlap_d [B] i32 or
+ * NULL, roll = 1 reads X rolled by 128. src/viterbi.hip:49-188,275-279 (k_viterbi_fwd). */
+int qtip_k_viterbi_fwd(const float* X_d, const int* overlap_d, int roll, int B, uint16_t* A_d,
+                       uint16_t* final_state_d, const uint32_t* lut_h2_d, void* stream);
+/* Pass-1 backtrace: overlap[b] = state(step 64) >> 4. src/viterbi.hip:197-205,280-283 (k_viterbi_overlap). */
+int qtip_k_viterbi_overlap(const uint16_t* A_d, const uint16_t* final_state_d, int B, int* overlap_d, void* stream);
+/* Pass-2 backtrace: states into Q_d[(b0+b)*nblk+blk][128] (may be NULL) and decoded values scattered into
+ * hatWT_d[(col0+c)*m + 16(b0+b)+r] (may be NULL). src/viterbi.hip:207-229,284-289 (k_viterbi_finish). */
+int qtip_k_viterbi_finish(const uint16_t* A_d, const uint16_t* final_state_d, int B, int b0, uint16_t* Q_d, int nblk,
+                          int blk, float* hatWT_d, long m, int col0, const uint32_t* lut_h2_d, void* stream);
+/* hat_d[b][2i..2i+1] = lut[states_d[b][i]]. src/viterbi.hip:231-238,290-294 (k_decode_states). */
+int qtip_k_decode_states(const uint16_t* states_d, int B, float* hat_d, const uint32_t* lut_h2_d, void* stream);
+
+/* Elementwise / layout kernels used around LDLQ and the weight rotation. src/gpu.hpp:222-259, src/kernels.hip:66-314. */
+int qtip_k_hadamard_rows(float* X_d, long rows, int n, long ld, int transpose, void* stream);
+int qtip_k_transpose(const float* in_d, long rows, long cols, long ld_in, float* out_d, long ld_out, void* stream);
+int qtip_k_scale_rows_cols(float* X_d, long rows, long cols, long ld, const float* rs_d, const float* cs_d,
+                           void* stream);
+int qtip_k_scale(float* X_d, long rows, long cols, long ld, float a, void* stream);
+int qtip_k_sub(const float* A_d, const float* B_d, float* D_d, long rows, long cols, long ld, void* stream);
+int qtip_k_sumsq(const float* X_d, long rows, long cols, long ld, double* out_d, void* stream);
+int qtip_k_dot(const float* A_d, long lda, const float* B_d, long ldb, long rows, long cols, double* out_d,
+               void* stream);
+int qtip_k_add_diag(float* H_d, long n, float a, void* stream);
+int qtip_k_diag_sum(const float* H_d, long n, double* out_d, void* stream);
+int qtip_k_split_bf16(const float* X_d, long rows, long cols, long ld_in, uint16_t* hi_d, uint16_t* lo_d,
+                      long ld_out, void* stream);
+int qtip_k_diff_split_bf16(const float* A_d, const float* B_d, long rows, long cols, long ld, uint16_t* hi_d,
+                           uint16_t* lo_d, long ld_out, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Encode side: fused interface (what a caller of ldlq_gpu / quantize_group switches to).
+ */
+/* Bytes of device workspace qtip_quantize_tiles needs for up to max_tiles sequences per call. */
+size_t qtip_quantize_workspace_bytes(int max_tiles);
+/* Two-pass tail-biting quantisation of B sequences: forward(roll) -> overlap -> forward(overlap) -> backtrace, the
+ * call sequence of src/quantizer.cpp:59-62 in one entry point. X_d [B][256] f32 -> states_d [B][128] u16 (may be
+ * NULL) and hat_d [B][256] f32 decoded values in sequence order (may be NULL). Bit-identical to the four k_* calls. */
+int qtip_quantize_tiles(const float* X_d, int B, const uint32_t* lut_h2_d, uint16_t* states_d, float* hat_d,
+                        void* workspace_d, size_t workspace_bytes, void* stream);
+/* Same, with the outputs of k_viterbi_finish: states into Q_d[(b0+b)*nblk+blk][128] and decoded values scattered
+ * through the tile permutation into hatWT_d[(col0+c)*m + 16(b0+b)+r]. Either may be NULL. */
+int qtip_quantize_tiles_scatter(const float* X_d, int B, int b0, const uint32_t* lut_h2_d, uint16_t* Q_d, int nblk,
+                                int blk, float* hatWT_d, long m, int col0, void* workspace_d, size_t workspace_bytes,
+                                void* stream);
+
+/* Synchronises `stream`, then returns QTIP_E_KERNEL if a fused call that used this workspace since its last reset
+ * reported a timed-out hand-shake between thread blocks (its outputs are then invalid), else QTIP_OK. Each fused call
+ * resets the status word when it starts. The reference has no counterpart: its kernels have no inter-block waits. */
+int qtip_workspace_status(const void* workspace_d, void* stream);
+
+/* Building blocks of the fused path, exported for profiling and for callers that keep their own scratch: the
+ * forward pass of k_viterbi_fwd (src/viterbi.hip:49-188) with the back-pointers stored as one 32-bit word per
+ * (8 steps, group): bp_d [B][16][4096] u32, word (b, i >> 3, j) holds step i of group j in bits [4 (7 - (i & 7)), +4);
+ * 8-step blocks below first_block are not written (pass 1 needs blocks 8..15 only). status_d: one int, set to 1 if a
+ * hand-shake timed out (zero it first). The two backtraces read that layout (k_viterbi_overlap / k_viterbi_finish,
+ * src/viterbi.hip:197-229); finish can also write the decoded values in sequence order to hat_d [B][256]. */
+int qtip_k_viterbi_fwd_words(const float* X_d, const int* overlap_d, int roll, int B, uint32_t* bp_d, int first_block,
+                             uint16_t* final_state_d, const uint32_t* lut_h2_d, int* status_d, void* stream);
+int qtip_k_viterbi_overlap_words(const uint32_t* bp_d, const uint16_t* final_state_d, int B, int* overlap_d,
+                                 void* stream);
+int qtip_k_viterbi_finish_words(const uint32_t* bp_d, const uint16_t* final_state_d, int B, int b0, uint16_t* Q_d,
+                                int nblk, int blk, float* hat_d, float* hatWT_d, long m, int col0,
+                                const uint32_t* lut_h2_d, void* stream);
+
+/* X_d[(tr * (n/16) + tc)][p] = W_d[16 tr + r][16 tc + c], 16 r + c = perm(p): the sequences of every 16x16 tile of a
+ * row-major m x n matrix (row stride ld), i.e. what k_ldlq_prep produces block by block when the Hessian is the
+ * identity (L = 0, prod = 0; src/viterbi.hip:241-267). */
+int qtip_tiles_from_matrix(const float* W_d, long m, long n, long ld, float* X_d, void* stream);
+
+/* Bytes of device workspace qtip_ldlq needs for an n x m problem (prod, X, Viterbi scratch). */
+size_t qtip_ldlq_workspace_bytes(long n, long m);
+/* LDLQ with 128-column buffers over WT_d (n x m f32, already scaled) and L_d (n x n f32, strictly block-lower):
+ * writes hatWT_d (n x m) and Q_d [(m/16)(n/16)][128]. Replaces ldlq_gpu (src/quantizer.cpp:30-89); the cross-buffer
+ * update is an fp32 FMA kernel instead of the split-bf16 library GEMM. Rows of W (columns j of WT) are independent:
+ * [j0, j0+mj) restricts the call to that slice of rows (multiple of 16) for row-block sharding over GPUs; pass
+ * j0 = 0, mj = m for the whole matrix. */
+int qtip_ldlq(const float* WT_d, const float* L_d, long n, long m, long j0, long mj, float* hatWT_d, uint16_t* Q_d,
+              const uint32_t* lut_h2_d, void* workspace_d, size_t workspace_bytes, void* stream);
+
+/* Bitstream and kernel layout on the device. src/qtip_core.cpp:194-253 (pack_trellis, unpack_trellis,
+ * swizzle_for_kernel, unswizzle_for_kernel; CPU code in the reference, src/quantizer.cpp:306-320). */
+int qtip_pack_trellis(const uint16_t* states_d, long B, uint16_t* packed_d, void* stream);
+int qtip_unpack_trellis(const uint16_t* packed_d, long B, uint16_t* states_d, void* stream);
+int qtip_swizzle_for_kernel(const uint16_t* packed_d, int m, int n, uint16_t* out_d, void* stream);
+int qtip_unswizzle_for_kernel(const uint16_t* in_d, int m, int n, uint16_t* packed_d, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Decode side: the runtime's QTIP linear operator. runtime/cuda/kernels.hpp:5-24, batch_kernels.hpp:5-8,22-23.
+ * bf16 values are passed as uint16_t bit patterns (the reference's B16).
+ */
+typedef struct qtip_matrix {
+  const uint16_t* trellis; /* _d kernel-layout words, (out/16)(in/16)*32 */
+  const float* su;         /* _d [in]  +-1 */
+  const float* sv;         /* _d [out] sign * Wscale */
+  const uint32_t* lut;     /* _d [1024] bf16x2 (qtip_runtime_lut) */
+  int in, out;
+} qtip_matrix; /* field for field runtime/cuda/kernels.hpp:5-10 (QtipMatrix) */
+
+/* rotated = bf16(hadUt_in(x * SU)). scratch_d >= max(in,out)*tokens f32, rotated_d >= in*tokens bf16.
+ * runtime/cuda/kernels.cu:412-427 (qtip_prepare). */
+int qtip_prepare(qtip_matrix w, const uint16_t* x_d, float* scratch_d, uint16_t* rotated_d, void* stream, int tokens,
+                 int rank_major);
+/* z[split][token][stride] = What . rotated (fp32 accumulate, bf16 LUT values), K split into `splits` slices.
+ * runtime/cuda/kernels.cu:428-436 (qtip_multiply). */
+int qtip_multiply(qtip_matrix w, const uint16_t* rotated_d, float* z_d, int stride, int splits, void* stream,
+                  int tokens);
+/* y = bf16(SV * hadU_out(sum_splits z)), optional bf16 rounding of z first.
+ * runtime/cuda/kernels.cu:437-456 (qtip_finish). */
+int qtip_finish(qtip_matrix w, const float* z_d, uint16_t* y_d, float* scratch_d, int round_z, int splits,
+                void* stream, int tokens, int rank_major);
+/* Same from bf16 z. runtime/cuda/kernels.cu:457-470 (qtip_finish_b16). */
+int qtip_finish_b16(qtip_matrix w, const uint16_t* z_d, uint16_t* y_d, float* scratch_d, int tokens, void* stream,
+                    int rank_major);
+/* prepare + multiply + finish for one token. runtime/cuda/kernels.cu:471-476 (qtip_forward). */
+int qtip_forward(qtip_matrix w, const uint16_t* x_d, uint16_t* y_d, float* scratch_d, uint16_t* rotated_d,
+                 float* z_d, int round_z, void* stream, int splits);
+/* Token-major activations, split-major fp32 products. runtime/cuda/batch_kernels.cu:701-736 (qtip_multiply_batch).
+ * `implementation` is accepted for signature compatibility and ignored (one code path per batch regime). */
+int qtip_multiply_batch(qtip_matrix w, const uint16_t* x_d, float* z_d, int stride, int splits, int tokens,
+                        void* stream, int implementation);
+/* Dense bf16 decode of the whole matrix, row-major [out][in]. runtime/cuda/batch_kernels.cu:23-46,737-740. */
+int qtip_decode_matrix(qtip_matrix w, uint16_t* out_d, void* stream);
+/* x[i] = sum over splits of x[split*n + i]. runtime/cuda/batch_kernels.cu:670-678,831-835 (reduce_products). */
+int qtip_reduce_products(float* x_d, size_t elements, int splits, void* stream);
+/* y = bf16(sum over splits * scale[i % width]) (scale may be NULL). batch_kernels.cu:684-693,836-839. */
+int qtip_reduce_to_b16(const float* x_d, const float* scale_d, uint16_t* y_d, size_t elements, int width, int splits,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QTIP_B200_H */

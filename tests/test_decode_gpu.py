@@ -1,0 +1,159 @@
+"""The trellis-decode linear operator against the oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden
+from test_viterbi_gpu import dev, u16
+
+pytestmark = pytest.mark.gpu
+
+
+def make_linear(gpu, n_in, n_out, seed, tl=None, sv_scale=1.0):
+    s = gpu.synth
+    tl = s.seeded_tlut(1).view(np.uint16) if tl is None else tl
+    tr = s.random_trellis(n_out, n_in, seed)
+    su, sv = s.signs(n_in, seed + 1), s.signs(n_out, seed + 2) * np.float32(sv_scale)
+    w = gpu.linear.Matrix(dev(tr), dev(su), dev(sv), gpu.linear.runtime_lut(tl), n_in, n_out)
+    return w, tr, su, sv, tl
+
+
+def bf16_dev(x):
+    bits = np.ascontiguousarray(x)
+    return torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+
+
+def rel_l2(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b) / np.linalg.norm(b))
+
+
+def test_runtime_lut_matches_reference_vectors(gpu, hyb):
+    tl, _, _ = hyb
+    g = golden("decode_ref.npz")
+    assert np.array_equal(gpu.linear.runtime_lut(tl).cpu().numpy().view(np.uint32), g["bf16x2"])
+    bad = tl.copy()
+    bad[5, 1] = 0x7C00  # +inf
+    with pytest.raises(gpu.QtipError):
+        gpu.linear.runtime_lut(bad)
+
+
+def test_decode_matrix_bit_exact(gpu, oracle, hyb):
+    tl, _, _ = hyb
+    g = golden("decode_ref.npz")
+    n_in, n_out = int(g["n_in"]), int(g["n_out"])
+    w = gpu.linear.Matrix(dev(g["trellis"]), dev(g["su"]), dev(g["sv"]), gpu.linear.runtime_lut(tl), n_in, n_out)
+    out = torch.empty((n_out, n_in), dtype=torch.bfloat16, device="cuda")
+    gpu.linear.qtip_decode_matrix(w, out)
+    dense = out.float().cpu().numpy()
+    assert np.array_equal(dense[32:96], g["rows_bf16"])  # the reference's decode_rows_bf16
+    assert np.array_equal(dense, oracle.decode_rows(g["trellis"], n_in, n_out, tl, 0, n_out, True))
+    # a wider matrix: more than one 256-column strip, and a ragged last strip
+    w2, tr2, _, _, tl2 = make_linear(gpu, 1024 + 96, 64, 31)
+    out2 = torch.empty((64, 1120), dtype=torch.bfloat16, device="cuda")
+    gpu.linear.qtip_decode_matrix(w2, out2)
+    assert np.array_equal(out2.float().cpu().numpy(), oracle.decode_rows(tr2, 1120, 64, tl2, 0, 64, True))
+
+
+@pytest.mark.parametrize("n_in,n_out,splits", [(384, 256, 1), (384, 256, 3), (1024, 128, 4), (12288, 64, 1),
+                                               (3584, 96, 2), (1024, 57344 // 16, 1)])
+def test_multiply_against_decoded_weights(gpu, oracle, n_in, n_out, splits):
+    """z = What . u with What the bit-exact decoded bf16 weights and u a bf16 vector: fp32 tensor-core accumulation vs
+    float64, rel-L2 <= 1e-5 (only the summation order differs)."""
+    w, tr, su, sv, tl = make_linear(gpu, n_in, n_out, 40 + splits)
+    u_bits = gpu.synth.f32_to_bf16_bits(np.random.default_rng(6).standard_normal(n_in).astype(np.float32))
+    z = torch.zeros((splits, n_out), dtype=torch.float32, device="cuda")
+    gpu.linear.qtip_multiply(w, bf16_dev(u_bits), z, n_out, splits, 1)
+    W = oracle.decode_rows(tr, n_in, n_out, tl, 0, n_out, True).astype(np.float64)
+    ref = W @ gpu.synth.bf16_bits_to_f32(u_bits).astype(np.float64)
+    assert rel_l2(z.sum(0).cpu().numpy(), ref) < 1e-5
+    z2 = torch.zeros_like(z)
+    gpu.linear.qtip_multiply(w, bf16_dev(u_bits), z2, n_out, splits, 1)
+    assert torch.equal(z, z2)  # deterministic reduction order
+
+
+@pytest.mark.parametrize("n_in,n_out", [(384, 256), (1024, 384), (12288, 1024), (3584, 12288 // 8)])
+def test_forward_against_reference_linear(gpu, oracle, n_in, n_out):
+    """prepare + multiply + finish vs reference_forward(device_rounding = true). bf16 outputs against the bf16-rounded
+    reference: rel-L2 < 1e-2 (one bf16 ulp is 4e-3); the fp32 products z against the oracle's z: rel-L2 <= 1e-3."""
+    w, tr, su, sv, tl = make_linear(gpu, n_in, n_out, 50, sv_scale=0.003)
+    x = (np.random.default_rng(9).standard_normal(n_in) * 0.1).astype(np.float32)
+    xb = gpu.synth.f32_to_bf16_bits(x)
+    y = torch.empty(n_out, dtype=torch.bfloat16, device="cuda")
+    rot = torch.empty(n_in, dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty(max(n_in, n_out), dtype=torch.float32, device="cuda")
+    for splits, round_z in ((1, False), (4, False), (2, True)):
+        z = torch.zeros((splits, n_out), dtype=torch.float32, device="cuda")
+        gpu.linear.qtip_forward(w, bf16_dev(xb), y, scratch, rot, z, round_z, splits)
+        yo, zo = oracle.reference_forward(tr, su, sv, tl, n_in, n_out, gpu.synth.bf16_bits_to_f32(xb), True, round_z,
+                                          want_z=True)
+        zz = z.sum(0).cpu().numpy()
+        if not round_z:
+            assert rel_l2(zz, zo[0]) < 1e-3
+        yo_b = gpu.synth.bf16_bits_to_f32(gpu.synth.f32_to_bf16_bits(yo[0]))
+        assert rel_l2(y.float().cpu().numpy(), yo_b) < 1e-2
+        assert np.abs(y.float().cpu().numpy() - yo_b).max() < 0.03 * np.abs(yo_b).max()
+
+
+def test_forward_against_reference_vectors(gpu, hyb):
+    """The committed outputs of the reference's reference_forward (in = 384, out = 256, three tokens)."""
+    tl, _, _ = hyb
+    g = golden("decode_ref.npz")
+    n_in, n_out = int(g["n_in"]), int(g["n_out"])
+    w = gpu.linear.Matrix(dev(g["trellis"]), dev(g["su"]), dev(g["sv"]), gpu.linear.runtime_lut(tl), n_in, n_out)
+    xb = gpu.synth.f32_to_bf16_bits(g["x"])
+    tokens = xb.shape[0]
+    rot = torch.empty((tokens, n_in), dtype=torch.bfloat16, device="cuda")
+    z = torch.zeros((2, tokens, n_out), dtype=torch.float32, device="cuda")
+    y = torch.empty((tokens, n_out), dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty(tokens * n_in, dtype=torch.float32, device="cuda")
+    gpu.linear.qtip_prepare(w, bf16_dev(xb), scratch, rot, tokens)
+    gpu.linear.qtip_multiply_batch(w, rot, z, n_out, 2, tokens)
+    gpu.linear.qtip_finish(w, z, y, scratch, False, 2, tokens)
+    # the fixture used fp32 x; the operator takes bf16 x: compare with tolerance of the input rounding (2^-9 relative)
+    assert rel_l2(y.float().cpu().numpy(), g["y_10"]) < 2e-2
+
+
+@pytest.mark.parametrize("tokens", [2, 8, 13, 16, 40])
+def test_multiply_batch(gpu, oracle, tokens):
+    n_in, n_out = 1024, 256
+    w, tr, su, sv, tl = make_linear(gpu, n_in, n_out, 60)
+    xb = gpu.synth.f32_to_bf16_bits(np.random.default_rng(tokens).standard_normal((tokens, n_in)).astype(np.float32))
+    z = torch.zeros((3, tokens, n_out), dtype=torch.float32, device="cuda")
+    gpu.linear.qtip_multiply_batch(w, bf16_dev(xb), z, n_out, 3, tokens)
+    W = oracle.decode_rows(tr, n_in, n_out, tl, 0, n_out, True).astype(np.float64)
+    ref = gpu.synth.bf16_bits_to_f32(xb).astype(np.float64) @ W.T
+    assert rel_l2(z.sum(0).cpu().numpy(), ref) < 1e-5
+    zr = z.clone()
+    gpu.linear.reduce_products(zr, tokens * n_out, 3)
+    assert torch.equal(zr[0], (z[0] + z[1]) + z[2])
+    yb = torch.empty((tokens, n_out), dtype=torch.bfloat16, device="cuda")
+    gpu.linear.reduce_to_b16(z, None, yb, tokens * n_out, n_out, 3)
+    assert np.array_equal(u16(yb.view(torch.int16)), gpu.synth.f32_to_bf16_bits(zr[0].cpu().numpy()))
+
+
+def test_row_sharded_multiply_equals_full(gpu):
+    """Rotated-row tensor parallelism: contiguous block-row shards of the trellis give the same z slices."""
+    n_in, n_out = 1024, 512
+    w, *_ = make_linear(gpu, n_in, n_out, 70)
+    ub = gpu.synth.f32_to_bf16_bits(np.random.default_rng(1).standard_normal(n_in).astype(np.float32))
+    z = torch.zeros(n_out, dtype=torch.float32, device="cuda")
+    gpu.linear.qtip_multiply(w, bf16_dev(ub), z, n_out, 1, 1)
+    for world in (2, 4):
+        parts = []
+        for r in range(world):
+            row0, rows = gpu.sharding.block_row_range(n_out, r, world)
+            zr = torch.zeros(rows, dtype=torch.float32, device="cuda")
+            gpu.linear.qtip_multiply(w.rows(row0, rows), bf16_dev(ub), zr, rows, 1, 1)
+            parts.append(zr)
+        assert torch.equal(torch.cat(parts), z)
+
+
+def test_geometry_errors(gpu):
+    w, *_ = make_linear(gpu, 384, 256, 80)
+    z = torch.zeros(256, dtype=torch.float32, device="cuda")
+    u = torch.zeros(384, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(gpu.QtipError) as e:
+        gpu.linear.qtip_multiply(w, u, z, 128, 1, 1)  # stride < out
+    assert e.value.code == -2
+    with pytest.raises(gpu.QtipError):
+        gpu.linear.qtip_multiply(w, u, z, 256, 33, 1)  # more than 32 splits
