@@ -7,6 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["tables.cu", "viterbi.cu", "ldlq.cu", "hadamard.cu", "elementwise.cu", "decode.cu"]
 LIB = os.path.join(HERE, "libqtip_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+EXTRA = os.environ.get("QTIP_NVCC_FLAGS", "").split()
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr", "-ccbin", "/usr/bin/g++"]
 
@@ -29,7 +30,7 @@ def build(force=False, verbose=False):
     procs = []
     for src in SOURCES:
         obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
-        cmd = [NVCC, *FLAGS, "-c", os.path.join(HERE, "csrc", src), "-o", obj]
+        cmd = [NVCC, *FLAGS, *EXTRA, "-c", os.path.join(HERE, "csrc", src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

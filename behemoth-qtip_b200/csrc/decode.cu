@@ -9,7 +9,7 @@
 // the tensor cores and the SIMT pipes only decode. The LUT is replicated 32 times (entry e, copy l at byte 128 e + 4 l,
 // 128 KiB) so that every lane reads its own bank: the lookup is the co-critical resource (32 lookups per clock per SM),
 // and a single-copy table would serialise on bank conflicts. Index arithmetic per state: v = window >> shift,
-// X = v * 2v + 2v (= 2 v (v + 1), whose bits 7..16 are the entry), address = (X & 0x1ff80) | 4 l.
+// y = v v + v (bits 6..15 are the entry), word index = 32 entry + l.
 // Eight warps share one work item (a block-row, or one K-split of it) and reduce through shared memory in a fixed order,
 // so results are deterministic; a CTA runs four items at a time and walks the item list persistently.
 #include <mma.h>
@@ -29,108 +29,118 @@ constexpr int kItemsPerCta = kGemmThreads / 32 / kWarpsPerItem;  // 4
 constexpr int kLutBytes = 1024 * 32 * 4;                         // 128 KiB, 32 copies
 constexpr int kChunk = 4;                                        // blocks loaded ahead per warp
 
-__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void group_sync(int group) {
-  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kWarpsPerItem * 32) : "memory");
+__device__ __forceinline__ void warps_sync(int id, int warps) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(warps * 32) : "memory");
 }
 
-// Decodes window u (word c << 16 | word c+1) into the four LUT words of states 4c..4c+3 (lane-private LUT copy).
-__device__ __forceinline__ void decode_window(uint32_t u, uint32_t lut_lane, uint32_t (&a)[4]) {
+// Decodes window u (word c << 16 | word c+1) into the four LUT words of states 4c..4c+3. lut is the replicated table
+// (entry e, copy l at word 32 e + l), so every lane reads its own bank. Bits above 15 of a shifted window do not reach
+// bits 6..15 of v (v + 1), which are the entry.
+__device__ __forceinline__ void decode_window(uint32_t u, const uint32_t* lut, uint32_t lane, uint32_t (&a)[4]) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const uint32_t v = u >> (16 - 4 * k);
-    const uint32_t t = v + v;
-    const uint32_t x = v * t + t;
-    a[k] = lds_u32(lut_lane + (x & 0x1ff80u));
+    const uint32_t y = v * v + v;
+    a[k] = lut[((y >> 6) & 1023u) * 32u + lane];
   }
 }
 
-// z[(split * tokens_total + token) * stride + row]; x: [tokens_total][in] bf16 (the rotated input). One launch covers
-// tokens [t0, t0 + tokens), tokens <= 8 NT: each group of 8 tokens is one MMA column block held in registers.
-template <int NT>
-__global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matrix w, const uint16_t* __restrict__ x,
-                                                                       float* __restrict__ z, int stride, int splits,
-                                                                       int tokens_total, int t0, int tokens) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem);
-  float* red = reinterpret_cast<float*>(smem + kLutBytes);  // [items][warps][NT*8 tokens][32 rows]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int grp = warp / kWarpsPerItem, wi = warp % kWarpsPerItem;
-  for (int i = tid; i < 1024 * 32; i += kGemmThreads) lut_s[i] = w.lut[i >> 5];
-  __syncthreads();
-  const uint32_t lut_lane = smem_u32(lut_s) + uint32_t(lane) * 4u;
-  const int g = lane >> 2, tg = lane & 3;
-  const int n2 = w.in / 32, n_items = (w.out / 32) * splits;
-  const uint2* codes = reinterpret_cast<const uint2*>(w.trellis);
-  const uint32_t* xw = reinterpret_cast<const uint32_t*>(x) + size_t(t0) * (w.in / 2);
-  const int in_words = w.in / 2;
-  float* my_red = red + size_t(grp) * kWarpsPerItem * (NT * 8) * 32;
+struct ItemCtx {
+  const uint2* codes;     // kernel-layout words as 8-byte units (word c of the four tiles of a block)
+  const uint32_t* xw;     // rotated input, bf16 pairs, first token of this launch
+  const uint4* xs;        // XS: the single token's B fragments, staged per block and lane quarter
+  const uint32_t* lut;
+  float* z;
+  int n2, in_words, stride, splits, tokens_total, t0, tokens;
+};
 
-  for (int item = blockIdx.x * kItemsPerCta + grp; item < n_items; item += gridDim.x * kItemsPerCta) {
-    const int br = item / splits, sp = item - br * splits;
-    const int k_lo = int(long(n2) * sp / splits), k_hi = int(long(n2) * (sp + 1) / splits);
-    const int span = k_hi - k_lo;
-    const int b_lo = k_lo + int(long(span) * wi / kWarpsPerItem), b_hi = k_lo + int(long(span) * (wi + 1) / kWarpsPerItem);
-    const uint2* row_codes = codes + size_t(br) * n2 * 32 + lane;
-    float acc[NT][2][4];
+// One work item = one 32-row block-row x one K-split, shared by `nw` warps (this is warp `wi` of them): each warp takes
+// a contiguous run of 32x32 blocks, then the partial sums are added in warp order through `red` and written to z.
+template <int NT, bool XS>
+__device__ __forceinline__ void run_item(const ItemCtx& c, int item, int nw, int wi, int bar_id, float* red) {
+  constexpr int RT = XS ? 1 : NT * 8;  // tokens kept per warp in the reduction buffer
+  const int lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
+  const int br = item / c.splits, sp = item - br * c.splits;
+  const int k_lo = int(long(c.n2) * sp / c.splits), k_hi = int(long(c.n2) * (sp + 1) / c.splits);
+  const int span = k_hi - k_lo;
+  const int b_lo = k_lo + int(long(span) * wi / nw), b_hi = k_lo + int(long(span) * (wi + 1) / nw);
+  float acc[NT][2][4];
 #pragma unroll
-    for (int t = 0; t < NT; ++t)
+  for (int t = 0; t < NT; ++t)
 #pragma unroll
-      for (int i1 = 0; i1 < 2; ++i1)
+    for (int i1 = 0; i1 < 2; ++i1)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) acc[t][i1][q] = 0.f;
+      for (int q = 0; q < 4; ++q) acc[t][i1][q] = 0.f;
 
-    uint2 cur[kChunk], nxt[kChunk];
+  // One 32x32 block: the lane's word of the four tiles, its neighbour's word, four windows, four MMAs per token group.
+  auto process = [&](uint2 own, int blk) {
+    const uint2 peer = make_uint2(__shfl_sync(0xffffffffu, own.x, (lane + 1) & 31),
+                                  __shfl_sync(0xffffffffu, own.y, (lane + 1) & 31));
+    uint4 xb;
+    if constexpr (XS) xb = c.xs[blk * 4 + tg];
 #pragma unroll
-    for (int q = 0; q < kChunk; ++q) nxt[q] = row_codes[size_t(min(b_lo + q, max(b_hi - 1, b_lo))) * 32];
-    for (int b0 = b_lo; b0 < b_hi; b0 += kChunk) {
+    for (int j1 = 0; j1 < 2; ++j1) {
+      // B fragments of the 16 input columns of tile column j1: token g, columns 2 tg and 2 tg + 8
+      uint32_t bf[NT][2];
+      if constexpr (XS) {
+        bf[0][0] = j1 ? xb.z : xb.x;
+        bf[0][1] = j1 ? xb.w : xb.y;
+      } else {
 #pragma unroll
-      for (int q = 0; q < kChunk; ++q) cur[q] = nxt[q];
-      if (b0 + kChunk < b_hi) {
-#pragma unroll
-        for (int q = 0; q < kChunk; ++q) nxt[q] = row_codes[size_t(min(b0 + kChunk + q, b_hi - 1)) * 32];
-      }
-#pragma unroll
-      for (int q = 0; q < kChunk; ++q) {
-        const int blk = b0 + q;
-        if (blk >= b_hi) break;
-        const uint2 own = cur[q];
-        const uint2 peer = make_uint2(__shfl_sync(0xffffffffu, own.x, (lane + 1) & 31),
-                                      __shfl_sync(0xffffffffu, own.y, (lane + 1) & 31));
-#pragma unroll
-        for (int j1 = 0; j1 < 2; ++j1) {
-          // B fragments of the 16 input columns of tile column j1: token g, columns 2 tg (+8)
-          uint32_t bf[NT][2];
-#pragma unroll
-          for (int t = 0; t < NT; ++t) {
-            const int token = t * 8 + g;
-            const uint32_t* xr = xw + size_t(min(token, tokens - 1)) * in_words + blk * 16 + j1 * 8 + tg;
-            bf[t][0] = __ldg(xr);
-            bf[t][1] = __ldg(xr + 4);
-          }
-          const uint32_t o = j1 ? own.y : own.x, p = j1 ? peer.y : peer.x;
-#pragma unroll
-          for (int i1 = 0; i1 < 2; ++i1) {
-            uint32_t a[4];
-            decode_window(__byte_perm(o, p, i1 ? 0x3276 : 0x1054), lut_lane, a);
-#pragma unroll
-            for (int t = 0; t < NT; ++t) mma_bf16_16816(acc[t][i1], a, bf[t][0], bf[t][1]);
-          }
+        for (int t = 0; t < NT; ++t) {
+          const uint32_t* xr = c.xw + size_t(min(t * 8 + g, c.tokens - 1)) * c.in_words + blk * 16 + j1 * 8 + tg;
+          bf[t][0] = __ldg(xr);
+          bf[t][1] = __ldg(xr + 4);
         }
       }
+      const uint32_t o = j1 ? own.y : own.x, p = j1 ? peer.y : peer.x;
+#pragma unroll
+      for (int i1 = 0; i1 < 2; ++i1) {
+        uint32_t a[4];
+        decode_window(__byte_perm(o, p, i1 ? 0x3276 : 0x1054), c.lut, uint32_t(lane), a);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) mma_bf16_16816(acc[t][i1], a, bf[t][0], bf[t][1]);
+      }
     }
-    // C fragment: c0 (row g, token 2tg), c1 (row g, token 2tg+1), c2 (row g+8, token 2tg), c3 (row g+8, token 2tg+1)
-    float* wr = my_red + size_t(wi) * (NT * 8) * 32;
+  };
+  // Two register sets of kChunk blocks alternate: one is consumed while the loads of the other are in flight.
+  const unsigned off0 = unsigned(br) * unsigned(c.n2) * 32u + unsigned(lane);
+  auto fetch = [&](uint2(&dst)[kChunk], int first) {
+#pragma unroll
+    for (int q = 0; q < kChunk; ++q) dst[q] = c.codes[off0 + unsigned(min(first + q, b_hi - 1)) * 32u];
+  };
+  auto consume = [&](const uint2(&src)[kChunk], int first) {
+#pragma unroll
+    for (int q = 0; q < kChunk; ++q)
+      if (first + q < b_hi) process(src[q], first + q);
+  };
+  if (b_lo < b_hi) {
+    uint2 bufA[kChunk], bufB[kChunk];
+    fetch(bufA, b_lo);
+    for (int b0 = b_lo; b0 < b_hi; b0 += 2 * kChunk) {
+      if (b0 + kChunk < b_hi) fetch(bufB, b0 + kChunk);
+      consume(bufA, b0);
+      if (b0 + 2 * kChunk < b_hi) fetch(bufA, b0 + 2 * kChunk);
+      if (b0 + kChunk < b_hi) consume(bufB, b0 + kChunk);
+    }
+  }
+  // C fragment: c0 (row g, token 2tg), c1 (row g, token 2tg+1), c2 (row g+8, token 2tg), c3 (row g+8, token 2tg+1)
+  float* wr = red + size_t(wi) * RT * 32;
+  if constexpr (XS) {
+    if (tg == 0) {
+#pragma unroll
+      for (int i1 = 0; i1 < 2; ++i1) {
+        wr[i1 * 16 + g] = acc[0][i1][0];
+        wr[i1 * 16 + g + 8] = acc[0][i1][2];
+      }
+    }
+  } else {
 #pragma unroll
     for (int t = 0; t < NT; ++t)
 #pragma unroll
@@ -141,18 +151,60 @@ __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matr
         wr[tok * 32 + row + 8] = acc[t][i1][2];
         wr[(tok + 1) * 32 + row + 8] = acc[t][i1][3];
       }
-    group_sync(grp);
-    for (int o = wi * 32 + lane; o < NT * 8 * 32; o += kWarpsPerItem * 32) {
-      const int tok = o >> 5, row = o & 31;
-      if (tok < tokens) {
-        float s = my_red[o];
-#pragma unroll
-        for (int q = 1; q < kWarpsPerItem; ++q) s += my_red[size_t(q) * (NT * 8) * 32 + o];
-        z[(size_t(sp) * tokens_total + t0 + tok) * stride + br * 32 + row] = s;
-      }
-    }
-    group_sync(grp);
   }
+  warps_sync(bar_id, nw);
+  for (int o = wi * 32 + lane; o < RT * 32; o += nw * 32) {
+    const int tok = o >> 5, row = o & 31;
+    if (tok < c.tokens) {
+      float s = red[o];
+      for (int q = 1; q < nw; ++q) s += red[size_t(q) * RT * 32 + o];
+      c.z[(size_t(sp) * c.tokens_total + c.t0 + tok) * c.stride + br * 32 + row] = s;
+    }
+  }
+  warps_sync(bar_id, nw);
+}
+
+// z[(split * tokens_total + token) * stride + row]; x: [tokens_total][in] bf16 (the rotated input). One launch covers
+// tokens [t0, t0 + tokens), tokens <= 8 NT: each group of 8 tokens is one MMA column block held in registers. XS (one
+// token): the activations are staged in shared memory in fragment order, one 16-byte read per block and lane.
+// Work items are dealt round-robin to groups of 8 warps (4 per CTA) for as many full rounds as there are; the remainder
+// is done by whole CTAs (32 warps per item) so that the tail of the launch is a quarter of a round long.
+template <int NT, bool XS>
+__global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matrix w, const uint16_t* __restrict__ x,
+                                                                       float* __restrict__ z, int stride, int splits,
+                                                                       int tokens_total, int t0, int tokens) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  constexpr int RT = XS ? 1 : NT * 8;
+  uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem);
+  float* red = reinterpret_cast<float*>(smem + kLutBytes);  // [32 warps][RT tokens][32 rows]
+  uint32_t* xs = reinterpret_cast<uint32_t*>(smem + kLutBytes + 32 * RT * 32 * 4);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  for (int i = tid; i < 1024 * 32; i += kGemmThreads) lut_s[i] = w.lut[i >> 5];
+  const uint32_t* xw = reinterpret_cast<const uint32_t*>(x) + size_t(t0) * (w.in / 2);
+  if constexpr (XS) {
+    for (int i = tid; i < w.in / 2; i += kGemmThreads) {
+      const int q = i & 15;  // word j1 * 8 + hi * 4 + tg of its block -> slot tg * 4 + j1 * 2 + hi
+      xs[(i & ~15) + (q & 3) * 4 + (q >> 3) * 2 + ((q >> 2) & 1)] = xw[i];
+    }
+  }
+  __syncthreads();
+  ItemCtx c;
+  c.codes = reinterpret_cast<const uint2*>(w.trellis);
+  c.xw = xw;
+  c.xs = reinterpret_cast<const uint4*>(xs);
+  c.lut = lut_s;
+  c.z = z;
+  c.n2 = w.in / 32, c.in_words = w.in / 2, c.stride = stride, c.splits = splits;
+  c.tokens_total = tokens_total, c.t0 = t0, c.tokens = tokens;
+  const int n_items = (w.out / 32) * splits;
+  const int slots = gridDim.x * kItemsPerCta;
+  const int n_grouped = n_items / slots * slots;
+  const int grp = warp / kWarpsPerItem, wi = warp % kWarpsPerItem;
+  for (int item = blockIdx.x * kItemsPerCta + grp; item < n_grouped; item += slots)
+    run_item<NT, XS>(c, item, kWarpsPerItem, wi, grp + 1, red + size_t(grp) * kWarpsPerItem * RT * 32);
+  __syncthreads();
+  for (int item = n_grouped + blockIdx.x; item < n_items; item += gridDim.x)
+    run_item<NT, XS>(c, item, kGemmThreads / 32, warp, 0, red);
 }
 
 // Dense decode to bf16, row-major [out][in]: a CTA decodes a 32-row x 256-column strip through shared memory so that
@@ -208,12 +260,17 @@ __global__ void reduce_b16_kernel(const float* x, const float* scale, uint16_t* 
   y[i] = f32_to_bf16(scale ? s * scale[i % width] : s);
 }
 
-template <int NT>
-static size_t gemm_smem() { return kLutBytes + size_t(kItemsPerCta) * kWarpsPerItem * (NT * 8) * 32 * 4; }
+constexpr size_t kMaxSmem = 227 * 1024;
+static size_t gemm_smem(int nt, bool xs, int n_in) {
+  return kLutBytes + size_t(32) * (xs ? 1 : nt * 8) * 32 * 4 + (xs ? size_t(n_in) * 2 : 0);
+}
 
 int decode_device_setup(DeviceInfo*) {
-  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm_smem<1>())));
-  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm_smem<2>())));
+  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMaxSmem)));
+  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               int(gemm_smem(1, false, 0))));
+  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               int(gemm_smem(2, false, 0))));
   return QTIP_OK;
 }
 
@@ -233,10 +290,15 @@ static int multiply_impl(qtip_matrix w, const uint16_t* x, float* z, int stride,
   const int per = tokens <= 8 ? 8 : 16;
   for (int t0 = 0; t0 < tokens; t0 += per) {
     const int nt = min(per, tokens - t0);
-    if (per == 8)
-      trellis_gemm_kernel<1><<<ctas, kGemmThreads, gemm_smem<1>(), s>>>(w, x, z, stride, splits, tokens, t0, nt);
+    if (tokens == 1 && gemm_smem(1, true, w.in) <= kMaxSmem)
+      trellis_gemm_kernel<1, true><<<ctas, kGemmThreads, gemm_smem(1, true, w.in), s>>>(w, x, z, stride, splits, tokens,
+                                                                                      t0, nt);
+    else if (per == 8)
+      trellis_gemm_kernel<1, false><<<ctas, kGemmThreads, gemm_smem(1, false, 0), s>>>(w, x, z, stride, splits, tokens,
+                                                                                      t0, nt);
     else
-      trellis_gemm_kernel<2><<<ctas, kGemmThreads, gemm_smem<2>(), s>>>(w, x, z, stride, splits, tokens, t0, nt);
+      trellis_gemm_kernel<2, false><<<ctas, kGemmThreads, gemm_smem(2, false, 0), s>>>(w, x, z, stride, splits, tokens,
+                                                                                      t0, nt);
     QB_LAUNCHED();
   }
   return QTIP_OK;

@@ -12,8 +12,8 @@
 //  * vit_fwd_cluster_kernel: the throughput path. An 8-CTA thread-block cluster owns the 65,536 states of the trellis
 //    (8,192 per SM, one group index j and its 16 predecessors d per thread), keeps each state's LUT pair and norm in
 //    registers for the whole launch, and runs 8 sequences at a time through them. The 4,096 group minima of a step are
-//    exchanged between the 8 SMs through distributed shared memory (each minimum is pushed to the one CTA that reads it
-//    next step) with mbarrier hand-shakes; the two 4-sequence halves of a batch alternate so that one half computes while
+//    exchanged between the 8 SMs through distributed shared memory (each minimum is pushed with st.async to the one CTA
+//    that reads it next step and counted on that CTA's mbarrier); the two 4-sequence halves of a batch alternate so that one half computes while
 //    the other half's minima are in flight. Back-pointers go to global memory as one 32-bit word per (8 steps, group).
 #include <cooperative_groups.h>
 
@@ -33,6 +33,16 @@ __device__ __forceinline__ float min3(float a, float b, float c) {
   asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
+// (bits & mask) | d in one LOP3. With the mask as an immediate the compiler needs two instructions (an immediate AND and
+// an immediate OR) on the half-rate integer pipe, which is the busiest pipe of the inner loop; the kernels therefore
+// take the mask (0xfffffff0) as a run-time argument so that it lives in a register and only d is an immediate.
+__device__ __forceinline__ float tag_cost(float c, uint32_t mask, int d) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(__float_as_uint(c)), "r"(mask), "r"(uint32_t(d)));
+  return __uint_as_float(r);
+}
+constexpr uint32_t kTagMask = 0xfffffff0u;
+
 // (cost, state) candidates of the last step order by cost, then by state.
 __device__ __forceinline__ void take_better(float& bv, uint32_t& bs, float ov, uint32_t os) {
   if (ov < bv || (ov == bv && os < bs)) bv = ov, bs = os;
@@ -46,7 +56,8 @@ __global__ __launch_bounds__(kTileThreads) void vit_fwd_tile_kernel(const float*
                                                                     const int* __restrict__ overlap, int roll,
                                                                     uint16_t* __restrict__ A,
                                                                     uint16_t* __restrict__ final_state,
-                                                                    const uint32_t* __restrict__ lut_h2) {
+                                                                    const uint32_t* __restrict__ lut_h2,
+                                                                    uint32_t tag_mask) {
   __shared__ float M[2][4096];
   __shared__ float xs[256];
   __shared__ float tl0[1024], tl1[1024], tnr[1024];  // compact LUT by entry (sign << 9 | index)
@@ -81,7 +92,7 @@ __global__ __launch_bounds__(kTileThreads) void vit_fwd_tile_kernel(const float*
       for (int q = 0; q < 4; ++q) {
         const uint32_t e = lut_entry(uint32_t((d << 12) | (t << 2) | q));
         const float c = state_cost(tl0[e], tl1[e], tnr[e], mp, m0, m1);
-        best[q] = fminf(best[q], __uint_as_float((__float_as_uint(c) & ~15u) | uint32_t(d)));
+        best[q] = fminf(best[q], tag_cost(c, tag_mask, d));
       }
     }
     uint32_t pk = 0;
@@ -182,10 +193,14 @@ __global__ void decode_states_kernel(const uint16_t* __restrict__ st, long n, fl
 constexpr int kCl = 8;          // CTAs per cluster; each owns 512 group indices j (8,192 states)
 constexpr int kClThreads = 512; // one j per thread
 constexpr int kTG = 4;          // sequences per half-batch (one float4 of minima per predecessor)
-constexpr int kNG = 2;          // half-batches in flight
+#ifndef QB_VIT_GROUPS
+#define QB_VIT_GROUPS 2
+#endif
+constexpr int kNG = QB_VIT_GROUPS;  // groups of kTG sequences in flight: one computes while the others' minima travel
 constexpr int kTB = kTG * kNG;  // sequences per cluster batch
 constexpr int kBufs = 3;        // exchange buffers per half-batch (see the hazard note in the kernel)
 constexpr long long kWaitCycles = 2000000000LL;  // give up a hand-shake after about a second
+constexpr uint32_t kBufBytes = 16 * 32 * kTG * 4;  // one exchange buffer
 
 struct __align__(16) ClusterSmem {
   // M[g][buf][d][gl][t]: minimum (+ next step's xx) of predecessor group (d << 8) | (32 * rank + gl) for sequence t of
@@ -207,8 +222,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t ran
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+// 16-byte store into a peer CTA's shared memory that, on delivery, counts 16 bytes on that CTA's mbarrier: data and
+// signal travel together, no fence on the sending side.
+__device__ __forceinline__ void st_async_v4(uint32_t addr, float a, float b, float c, float d, uint32_t bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(addr),
+               "f"(a), "f"(b), "f"(c), "f"(d), "r"(bar)
                : "memory");
 }
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float a) {
@@ -220,14 +238,15 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t addr, uint32_t a) {
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+// Arms the next phase of a local mbarrier: one arrival (this one) plus `bytes` of incoming st.async traffic.
+__device__ __forceinline__ void mbar_arm(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -244,7 +263,10 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void wait_full(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
   if (mbar_try_wait(bar, parity)) return;
   const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
+  for (;;) {
+#pragma unroll 1
+    for (int spin = 0; spin < 256; ++spin)
+      if (mbar_try_wait(bar, parity)) return;
     if (*abort_flag) return;
     if (clock64() - start > kWaitCycles) {
       *abort_flag = 1;
@@ -258,7 +280,8 @@ __device__ __forceinline__ void wait_full(uint32_t bar, uint32_t parity, volatil
 // j in bits [4 (7 - (i & 7)), +4); blocks below first_blk are not stored. final_state [B].
 __global__ __cluster_dims__(kCl, 1, 1) __launch_bounds__(kClThreads, 1) void vit_fwd_cluster_kernel(
     const float* __restrict__ X, const int* __restrict__ overlap, int roll, int B, uint32_t* __restrict__ bp,
-    int first_blk, uint16_t* __restrict__ final_state, const uint32_t* __restrict__ lut_h2, int* __restrict__ status) {
+    int first_blk, uint16_t* __restrict__ final_state, const uint32_t* __restrict__ lut_h2, int* __restrict__ status,
+    uint32_t tag_mask) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   ClusterSmem& sm = *reinterpret_cast<ClusterSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -279,9 +302,12 @@ __global__ __cluster_dims__(kCl, 1, 1) __launch_bounds__(kClThreads, 1) void vit
 
   if (tid == 0) {
     for (int g = 0; g < kNG; ++g)
-      for (int b = 0; b < kBufs; ++b) mbar_init(smem_u32(&sm.full[g][b]), 2 * kCl);  // 2 warps from each CTA
+      for (int b = 0; b < kBufs; ++b) mbar_init(smem_u32(&sm.full[g][b]), 1);
     sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // Every phase of every barrier receives one full buffer: 16 x 32 rows of kTG floats from the 8 CTAs.
+    for (int g = 0; g < kNG; ++g)
+      for (int b = 0; b < kBufs; ++b) mbar_arm(smem_u32(&sm.full[g][b]), kBufBytes);
   }
   cluster_sync_all();
 
@@ -291,7 +317,7 @@ __global__ __cluster_dims__(kCl, 1, 1) __launch_bounds__(kClThreads, 1) void vit
   const int dprime = int(rank) * 2 + (warp >> 3);
   const uint32_t push_base = map_to_cta(smem_u32(&sm.M[0][0][dprime][lane][0]), dst);
   const uint32_t bar_base = map_to_cta(smem_u32(&sm.full[0][0]), dst);
-  constexpr uint32_t kBufBytes = 16 * 32 * kTG * 4, kGrpBytes = kBufs * kBufBytes;
+  constexpr uint32_t kGrpBytes = kBufs * kBufBytes;
   volatile int* abort_flag = &sm.abort_flag;
   uint32_t phase_bits = 0;  // bit g * kBufs + buf: parity of the next wait on full[g][buf]
 
@@ -299,13 +325,13 @@ __global__ __cluster_dims__(kCl, 1, 1) __launch_bounds__(kClThreads, 1) void vit
     const int t_first = batch * kTB;
     // Per-step input terms of the kTB sequences (sequences past B repeat the last one and are not stored).
     for (int idx = tid; idx < 128 * kTB; idx += kClThreads) {
-      const int tl = idx & (kTB - 1), step = idx >> 3;
+      const int tl = idx % kTB, step = idx / kTB;
       const float* src = X + size_t(min(t_first + tl, B - 1)) * 256;
       const int p0 = roll ? ((2 * step + 128) & 255) : 2 * step;
       const float x0 = round_half(src[p0]), x1 = round_half(src[p0 + 1]);
-      sm.m01[step][tl >> 2][0][tl & 3] = round_half(-2.f * x0);
-      sm.m01[step][tl >> 2][1][tl & 3] = round_half(-2.f * x1);
-      sm.xx[step][tl >> 2][tl & 3] = __fadd_rn(__fmul_rn(x0, x0), __fmul_rn(x1, x1));
+      sm.m01[step][tl / kTG][0][tl % kTG] = round_half(-2.f * x0);
+      sm.m01[step][tl / kTG][1][tl % kTG] = round_half(-2.f * x1);
+      sm.xx[step][tl / kTG][tl % kTG] = __fadd_rn(__fmul_rn(x0, x0), __fmul_rn(x1, x1));
     }
     if (tid < kTB) sm.ov[tid] = overlap ? overlap[min(t_first + tid, B - 1)] : -1;
     __syncthreads();
@@ -338,6 +364,7 @@ __global__ __cluster_dims__(kCl, 1, 1) __launch_bounds__(kClThreads, 1) void vit
           const uint32_t bit = uint32_t(g * kBufs + buf);
           wait_full(smem_u32(&sm.full[g][buf]), (phase_bits >> bit) & 1u, abort_flag, status);
           phase_bits ^= 1u << bit;
+          if (tid == 0) mbar_arm(smem_u32(&sm.full[g][buf]), kBufBytes);  // for this buffer's next use
         }
         const float4 m0 = *reinterpret_cast<const float4*>(&sm.m01[i][g][0][0]);
         const float4 m1 = *reinterpret_cast<const float4*>(&sm.m01[i][g][1][0]);
@@ -352,8 +379,7 @@ __global__ __cluster_dims__(kCl, 1, 1) __launch_bounds__(kClThreads, 1) void vit
           for (int t = 0; t < 4; ++t) {
             const float ca = state_cost(l0[d], l1[d], nr[d], paa[t], m0a[t], m1a[t]);
             const float cb = state_cost(l0[d + 1], l1[d + 1], nr[d + 1], pba[t], m0a[t], m1a[t]);
-            best[t] = min3(best[t], __uint_as_float((__float_as_uint(ca) & ~15u) | uint32_t(d)),
-                           __uint_as_float((__float_as_uint(cb) & ~15u) | uint32_t(d + 1)));
+            best[t] = min3(best[t], tag_cost(ca, tag_mask, d), tag_cost(cb, tag_mask, d + 1));
           }
         }
         const float4 xn = *reinterpret_cast<const float4*>(&sm.xx[i + 1][g][0]);
@@ -362,12 +388,11 @@ __global__ __cluster_dims__(kCl, 1, 1) __launch_bounds__(kClThreads, 1) void vit
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           const uint32_t bb = __float_as_uint(best[t]);
-          hist[g * kTG + t] = (hist[g * kTG + t] << 4) | (bb & 15u);
+          hist[g * kTG + t] = hist[g * kTG + t] * 16u + (bb & 15u);  // multiply-add: keeps the shift off the integer pipe
           out[t] = __fadd_rn(__uint_as_float(bb & ~15u), xna[t]);
         }
-        st_cluster_v4(push_base + uint32_t(g) * kGrpBytes + uint32_t(nbuf) * kBufBytes, out[0], out[1], out[2], out[3]);
-        __syncwarp();
-        if (lane == 0) mbar_arrive_remote(bar_base + uint32_t(g * kBufs + nbuf) * 8u);
+        st_async_v4(push_base + uint32_t(g) * kGrpBytes + uint32_t(nbuf) * kBufBytes, out[0], out[1], out[2], out[3],
+                    bar_base + uint32_t(g * kBufs + nbuf) * 8u);
       }
       if ((i & 7) == 7 || i == 126) {
         const int blk = i >> 3;
@@ -388,6 +413,7 @@ __global__ __cluster_dims__(kCl, 1, 1) __launch_bounds__(kClThreads, 1) void vit
         const uint32_t bit = uint32_t(g * kBufs + buf);
         wait_full(smem_u32(&sm.full[g][buf]), (phase_bits >> bit) & 1u, abort_flag, status);
         phase_bits ^= 1u << bit;
+        if (tid == 0) mbar_arm(smem_u32(&sm.full[g][buf]), kBufBytes);
         const float4 m0 = *reinterpret_cast<const float4*>(&sm.m01[127][g][0][0]);
         const float4 m1 = *reinterpret_cast<const float4*>(&sm.m01[127][g][1][0]);
         const float m0a[4] = {m0.x, m0.y, m0.z, m0.w}, m1a[4] = {m1.x, m1.y, m1.z, m1.w};
@@ -504,7 +530,7 @@ static size_t ws_bytes_for(size_t cap) {
 }
 static bool carve_workspace(void* ws, size_t bytes, QuantWorkspace* out) {
   if (!ws || bytes < ws_bytes_for(kTB)) return false;
-  size_t cap = (bytes - kWsHeader - 512) / (kBpBytes + 6);
+  size_t cap = (bytes - kWsHeader) / kBpBytes;
   while (cap > 0 && ws_bytes_for(cap) > bytes) --cap;
   if (cap < size_t(kTB)) return false;
   cap = cap / kTB * kTB;
@@ -526,7 +552,8 @@ static int launch_cluster_fwd(const DeviceInfo* info, const float* X, const int*
   const int batches = (B + kTB - 1) / kTB;
   const int clusters = batches < info->max_clusters ? batches : info->max_clusters;
   vit_fwd_cluster_kernel<<<dim3(clusters * kCl), dim3(kClThreads), sizeof(ClusterSmem), s>>>(X, overlap, roll, B, bp,
-                                                                                             first_blk, fs, lut, status);
+                                                                                             first_blk, fs, lut, status,
+                                                                                             kTagMask);
   QB_LAUNCHED();
   return QTIP_OK;
 }
@@ -565,7 +592,7 @@ extern "C" int qtip_k_viterbi_fwd(const float* X_d, const int* overlap_d, int ro
   QB_REQUIRE(X_d && A_d && final_state_d && lut_h2_d && B >= 0, QTIP_E_ARG, "qtip_k_viterbi_fwd: bad argument");
   if (B == 0) return QTIP_OK;
   vit_fwd_tile_kernel<<<unsigned(B), kTileThreads, 0, as_stream(stream)>>>(X_d, overlap_d, roll, A_d, final_state_d,
-                                                                          lut_h2_d);
+                                                                          lut_h2_d, kTagMask);
   QB_LAUNCHED();
   return QTIP_OK;
 }
@@ -633,8 +660,8 @@ extern "C" size_t qtip_quantize_workspace_bytes(int max_tiles) {
 }
 extern "C" int qtip_quantize_tiles(const float* X_d, int B, const uint32_t* lut_h2_d, uint16_t* states_d, float* hat_d,
                                    void* workspace_d, size_t workspace_bytes, void* stream) {
-  QB_REQUIRE(X_d && lut_h2_d && B >= 0, QTIP_E_ARG, "qtip_quantize_tiles: bad argument");
   if (B == 0) return QTIP_OK;
+  QB_REQUIRE(X_d && lut_h2_d && B > 0, QTIP_E_ARG, "qtip_quantize_tiles: bad argument");
   return quantize_tiles_impl(X_d, B, 0, lut_h2_d, states_d, 1, 0, hat_d, nullptr, 0, 0, workspace_d, workspace_bytes,
                              as_stream(stream));
 }
