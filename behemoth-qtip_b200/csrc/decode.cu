@@ -27,7 +27,10 @@ constexpr int kGemmThreads = 1024;
 constexpr int kWarpsPerItem = 8;
 constexpr int kItemsPerCta = kGemmThreads / 32 / kWarpsPerItem;  // 4
 constexpr int kLutBytes = 1024 * 32 * 4;                         // 128 KiB, 32 copies
-constexpr int kChunk = 4;                                        // blocks loaded ahead per warp
+#ifndef QB_GEMV_CHUNK
+#define QB_GEMV_CHUNK 4
+#endif
+constexpr int kChunk = QB_GEMV_CHUNK;  // blocks per register set; two sets alternate, so up to 2 kChunk loads are in flight per warp
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -39,23 +42,27 @@ __device__ __forceinline__ void warps_sync(int id, int warps) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(warps * 32) : "memory");
 }
 
-// Decodes window u (word c << 16 | word c+1) into the four LUT words of states 4c..4c+3. lut is the replicated table
+// Dynamic shared memory of the GEMM kernel, named at namespace scope so that every access is known to be a
+// shared-memory access at a constant base (a pointer carried through a struct is not): words [0, 32768) hold the
+// replicated LUT.
+extern __shared__ __align__(16) uint32_t gemm_smem_words[];
+
+// Decodes window u (word c << 16 | word c+1) into the four LUT words of states 4c..4c+3 from the replicated table
 // (entry e, copy l at word 32 e + l), so every lane reads its own bank. Bits above 15 of a shifted window do not reach
 // bits 6..15 of v (v + 1), which are the entry.
-__device__ __forceinline__ void decode_window(uint32_t u, const uint32_t* lut, uint32_t lane, uint32_t (&a)[4]) {
+__device__ __forceinline__ void decode_window(uint32_t u, uint32_t lane, uint32_t (&a)[4]) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const uint32_t v = u >> (16 - 4 * k);
     const uint32_t y = v * v + v;
-    a[k] = lut[((y >> 6) & 1023u) * 32u + lane];
+    a[k] = gemm_smem_words[((y >> 6) & 1023u) * 32u + lane];
   }
 }
 
 struct ItemCtx {
   const uint2* codes;     // kernel-layout words as 8-byte units (word c of the four tiles of a block)
   const uint32_t* xw;     // rotated input, bf16 pairs, first token of this launch
-  const uint4* xs;        // XS: the single token's B fragments, staged per block and lane quarter
-  const uint32_t* lut;
+  int xs_word;            // XS: word offset in shared memory of the single token's B fragments (16 B per block and lane quarter)
   float* z;
   int n2, in_words, stride, splits, tokens_total, t0, tokens;
 };
@@ -83,7 +90,7 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, int item, int nw, int
     const uint2 peer = make_uint2(__shfl_sync(0xffffffffu, own.x, (lane + 1) & 31),
                                   __shfl_sync(0xffffffffu, own.y, (lane + 1) & 31));
     uint4 xb;
-    if constexpr (XS) xb = c.xs[blk * 4 + tg];
+    if constexpr (XS) xb = reinterpret_cast<const uint4*>(gemm_smem_words + c.xs_word)[blk * 4 + tg];
 #pragma unroll
     for (int j1 = 0; j1 < 2; ++j1) {
       // B fragments of the 16 input columns of tile column j1: token g, columns 2 tg and 2 tg + 8
@@ -103,7 +110,7 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, int item, int nw, int
 #pragma unroll
       for (int i1 = 0; i1 < 2; ++i1) {
         uint32_t a[4];
-        decode_window(__byte_perm(o, p, i1 ? 0x3276 : 0x1054), c.lut, uint32_t(lane), a);
+        decode_window(__byte_perm(o, p, i1 ? 0x3276 : 0x1054), uint32_t(lane), a);
 #pragma unroll
         for (int t = 0; t < NT; ++t) mma_bf16_16816(acc[t][i1], a, bf[t][0], bf[t][1]);
       }
@@ -173,9 +180,9 @@ template <int NT, bool XS>
 __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matrix w, const uint16_t* __restrict__ x,
                                                                        float* __restrict__ z, int stride, int splits,
                                                                        int tokens_total, int t0, int tokens) {
-  extern __shared__ __align__(16) unsigned char smem[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(gemm_smem_words);
   constexpr int RT = XS ? 1 : NT * 8;
-  uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem);
+  uint32_t* lut_s = gemm_smem_words;
   float* red = reinterpret_cast<float*>(smem + kLutBytes);  // [32 warps][RT tokens][32 rows]
   uint32_t* xs = reinterpret_cast<uint32_t*>(smem + kLutBytes + 32 * RT * 32 * 4);
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -191,8 +198,7 @@ __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matr
   ItemCtx c;
   c.codes = reinterpret_cast<const uint2*>(w.trellis);
   c.xw = xw;
-  c.xs = reinterpret_cast<const uint4*>(xs);
-  c.lut = lut_s;
+  c.xs_word = (kLutBytes + 32 * RT * 32 * 4) / 4;
   c.z = z;
   c.n2 = w.in / 32, c.in_words = w.in / 2, c.stride = stride, c.splits = splits;
   c.tokens_total = tokens_total, c.t0 = t0, c.tokens = tokens;
