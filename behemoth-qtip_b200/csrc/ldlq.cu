@@ -13,7 +13,8 @@
 namespace qb {
 
 int quantize_tiles_impl(const float* X, int B, int b0, const uint32_t* lut, uint16_t* Q, int nblk, int blk, float* hat,
-                        float* hatWT, long m, int col0, void* ws, size_t ws_bytes, cudaStream_t s);  // viterbi.cu
+                        float* hatWT, long m, int col0, void* ws, size_t ws_bytes, bool reset_status,
+                        cudaStream_t s);  // viterbi.cu
 
 // Rows j in [j0, j0 + mj) of W; X is indexed from the slice start: X[(j - j0) >> 4][256].
 __global__ __launch_bounds__(256) void ldlq_prep_kernel(const float* __restrict__ WT, const float* __restrict__ hatWT,
@@ -121,7 +122,7 @@ extern "C" int qtip_k_ldlq_prep(const float* WT_d, const float* hatWT_d, const f
 extern "C" size_t qtip_ldlq_workspace_bytes(long n, long m) {
   if (n <= 0 || m <= 0) return 0;
   const long ntr = m / 16;
-  return align256(size_t(n) * m * 4) + align256(size_t(ntr) * 256 * 4) + qtip_quantize_workspace_bytes(int(ntr));
+  return qtip_quantize_workspace_bytes(int(ntr)) + align256(size_t(n) * m * 4) + align256(size_t(ntr) * 256 * 4);
 }
 
 extern "C" int qtip_ldlq(const float* WT_d, const float* L_d, long n, long m, long j0, long mj, float* hatWT_d,
@@ -133,17 +134,19 @@ extern "C" int qtip_ldlq(const float* WT_d, const float* L_d, long n, long m, lo
   QB_REQUIRE(j0 >= 0 && mj > 0 && j0 % 16 == 0 && mj % 16 == 0 && j0 + mj <= m, QTIP_E_GEOMETRY,
              "LDLQ row slice [%ld, %ld) must be whole 16-row blocks inside m = %ld", j0, j0 + mj, m);
   cudaStream_t s = as_stream(stream);
-  // The workspace holds prod for the full n x m extent (only the slice's columns are touched), the slice's sequences
-  // and the Viterbi scratch.
+  // Workspace: [Viterbi scratch, status word first][prod, full n x m extent, only the slice's columns are touched]
+  // [the slice's sequences]. qtip_workspace_status() therefore works on an LDLQ workspace too.
   const size_t prod_bytes = align256(size_t(n) * m * 4), x_bytes = align256(size_t(mj / 16) * 256 * 4);
-  QB_REQUIRE(workspace_bytes >= prod_bytes + x_bytes + qtip_quantize_workspace_bytes(8), QTIP_E_WORKSPACE,
-             "qtip_ldlq: workspace of %zu bytes is too small", workspace_bytes);
+  const size_t vws_bytes = qtip_quantize_workspace_bytes(int(mj / 16));
+  QB_REQUIRE(workspace_bytes >= vws_bytes + prod_bytes + x_bytes, QTIP_E_WORKSPACE,
+             "qtip_ldlq: workspace of %zu bytes is too small (need %zu)", workspace_bytes,
+             vws_bytes + prod_bytes + x_bytes);
   unsigned char* p = static_cast<unsigned char*>(workspace_d);
-  float* prod = reinterpret_cast<float*>(p);
-  float* X = reinterpret_cast<float*>(p + prod_bytes);
-  void* vws = p + prod_bytes + x_bytes;
-  const size_t vws_bytes = workspace_bytes - prod_bytes - x_bytes;
+  void* vws = p;
+  float* prod = reinterpret_cast<float*>(p + vws_bytes);
+  float* X = reinterpret_cast<float*>(p + vws_bytes + prod_bytes);
   const int ntr = int(mj / 16), nblk = int(n / 16);
+  QB_CUDA(cudaMemsetAsync(vws, 0, 256, s));  // the status word; it then accumulates over all column steps
   zero_cols_kernel<<<148 * 8, 256, 0, s>>>(prod, n, m, j0, mj);
   QB_LAUNCHED();
   zero_cols_kernel<<<148 * 8, 256, 0, s>>>(hatWT_d, n, m, j0, mj);
@@ -155,7 +158,7 @@ extern "C" int qtip_ldlq(const float* WT_d, const float* L_d, long n, long m, lo
       ldlq_prep_kernel<<<blocks_for(mj, 256), 256, 0, s>>>(WT_d, hatWT_d, prod, L_d, n, m, j0, mj, col0, bufend, X);
       QB_LAUNCHED();
       int rc = quantize_tiles_impl(X, ntr, int(j0 / 16), lut_h2_d, Q_d, nblk, col0 / 16, nullptr, hatWT_d, m, col0, vws,
-                                   vws_bytes, s);
+                                   vws_bytes, false, s);
       if (rc) return rc;
     }
     if (c0 > 0) {

@@ -560,13 +560,13 @@ static int launch_cluster_fwd(const DeviceInfo* info, const float* X, const int*
 
 // Shared body of the two fused entry points.
 int quantize_tiles_impl(const float* X, int B, int b0, const uint32_t* lut, uint16_t* Q, int nblk, int blk, float* hat,
-                        float* hatWT, long m, int col0, void* ws, size_t ws_bytes, cudaStream_t s) {
+                        float* hatWT, long m, int col0, void* ws, size_t ws_bytes, bool reset_status, cudaStream_t s) {
   const DeviceInfo* info = device_info();
   if (!info) return QTIP_E_DEVICE;
   QuantWorkspace w;
   QB_REQUIRE(carve_workspace(ws, ws_bytes, &w), QTIP_E_WORKSPACE,
              "workspace of %zu bytes is too small (need at least %zu)", ws_bytes, ws_bytes_for(kTB));
-  QB_CUDA(cudaMemsetAsync(w.status, 0, kWsHeader, s));
+  if (reset_status) QB_CUDA(cudaMemsetAsync(w.status, 0, kWsHeader, s));
   for (int c0 = 0; c0 < B; c0 += w.cap) {
     const int nb = B - c0 < w.cap ? B - c0 : w.cap;
     const float* xc = X + size_t(c0) * 256;
@@ -663,7 +663,7 @@ extern "C" int qtip_quantize_tiles(const float* X_d, int B, const uint32_t* lut_
   if (B == 0) return QTIP_OK;
   QB_REQUIRE(X_d && lut_h2_d && B > 0, QTIP_E_ARG, "qtip_quantize_tiles: bad argument");
   return quantize_tiles_impl(X_d, B, 0, lut_h2_d, states_d, 1, 0, hat_d, nullptr, 0, 0, workspace_d, workspace_bytes,
-                             as_stream(stream));
+                             true, as_stream(stream));
 }
 extern "C" int qtip_quantize_tiles_scatter(const float* X_d, int B, int b0, const uint32_t* lut_h2_d, uint16_t* Q_d,
                                            int nblk, int blk, float* hatWT_d, long m, int col0, void* workspace_d,
@@ -674,7 +674,7 @@ extern "C" int qtip_quantize_tiles_scatter(const float* X_d, int B, int b0, cons
              "qtip_quantize_tiles_scatter: m = %ld does not cover %d row blocks", m, b0 + B);
   if (B == 0) return QTIP_OK;
   return quantize_tiles_impl(X_d, B, b0, lut_h2_d, Q_d, nblk, blk, nullptr, hatWT_d, m, col0, workspace_d,
-                             workspace_bytes, as_stream(stream));
+                             workspace_bytes, true, as_stream(stream));
 }
 extern "C" int qtip_workspace_status(const void* workspace_d, void* stream) {
   QB_REQUIRE(workspace_d, QTIP_E_ARG, "qtip_workspace_status: null workspace");

@@ -26,6 +26,7 @@ sys.path.insert(0, ROOT)
 M, N_COLS = 12288, 12288
 LANE_OPS_PER_WEIGHT = 327680  # 2 passes x 128 steps x 65,536 states / 256 weights x 5 ops (add, 2 fma, tag, min)
 METRIC = "viterbi_quantized_weights_per_second"
+NCU_DRAM_BYTES_PER_TILE_PASS = 9104128 // 240  # dram read + write of one 240-sequence launch (profiles/)
 
 
 def measured_peaks():
@@ -286,7 +287,9 @@ def main():
             "roofline": {"bound": "fp32_issue", "kernel": "vit_fwd_cluster_kernel", "achieved": achieved / 1e12,
                          "peak": peak_ops / 1e12, "unit": "Tlane-op/s", "frac": achieved / peak_ops,
                          "peak_source": "%d SMs x 128 lanes x sm_max_mhz of MEASURED_PEAKS.json (%s)" % (sm_count, peak_src),
-                         "ms_per_launch": kern_ms, "tiles_per_launch": nb, "traffic": None,
+                         "ms_per_launch": kern_ms, "tiles_per_launch": nb,
+                         "traffic": nb * NCU_DRAM_BYTES_PER_TILE_PASS,
+                         "traffic_note": "DRAM bytes of a 240-sequence ncu capture scaled by sequences (lower bound)",
                          "frac_at_sampled_clock": (achieved / (sm_count * 128 * clocks["sm_mhz"] * 1e6)
                                                    if clocks and clocks.get("sm_mhz") else None)}}
     if not args.no_extras:
