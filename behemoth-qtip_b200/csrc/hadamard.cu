@@ -76,25 +76,58 @@ struct HadArgs {
   float scale;
 };
 
+// Element offset of column element j of `row` relative to the source base: row-major, or [rank][row][n / ranks] when
+// the source was gathered from `ranks` ranks.
+__device__ __forceinline__ long src_offset(const HadArgs& a, long row, int j) {
+  if (a.ranks <= 1) return row * a.ld + j;
+  const int part = a.n / a.ranks, r = j / part;
+  return (long(r) * a.rows + row) * part + (j - r * part);
+}
 template <Mode M>
-__device__ __forceinline__ float load_src(const HadArgs& a, long row, int j) {
-  long at = row * a.ld + j;
-  if (a.ranks > 1) {
-    const int part = a.n / a.ranks, r = j / part;
-    at = (long(r) * a.rows + row) * part + (j - r * part);
-  }
-  if constexpr (M == Mode::F32Inplace) {
-    return static_cast<const float*>(a.src)[at];
-  } else if constexpr (M == Mode::Prepare) {
-    return bf16_to_f32(static_cast<const uint16_t*>(a.src)[at]) * a.sign[j];
-  } else if constexpr (M == Mode::Finish) {
-    const float* z = static_cast<const float*>(a.src);
-    float v = z[at];
-    for (int p = 1; p < a.splits; ++p) v += z[size_t(p) * a.split_stride + at];
-    if (a.round_z) v = bf16_to_f32(f32_to_bf16(v));
-    return v;
+__device__ __forceinline__ float load_one(const void* src, long at) {
+  if constexpr (M == Mode::F32Inplace || M == Mode::Finish) return static_cast<const float*>(src)[at];
+  else return bf16_to_f32(static_cast<const uint16_t*>(src)[at]);
+}
+// The K source values of column i (elements k P + i), loaded as one batch: the K loads of a pass are independent
+// straight-line code, so they are all in flight together (per-element control flow around each load would serialise
+// them on memory latency). K-split partials are added in split order, then optionally rounded to bf16.
+template <int K, Mode M>
+__device__ __forceinline__ void load_column(const HadArgs& a, long row, int i, int P, float (&v)[K]) {
+  if (a.ranks <= 1) {
+    const long base = row * a.ld + i;
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] = load_one<M>(a.src, base + k * P);
+    if constexpr (M == Mode::Finish) {
+      for (int p = 1; p < a.splits; ++p) {
+        const float* zp = static_cast<const float*>(a.src) + size_t(p) * a.split_stride + base;
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          v[k] += zp[k * P];
+          if (k % 8 == 7) asm volatile("" ::: "memory");  // at most 8 partial loads in flight: bounds register use
+        }
+      }
+    }
   } else {
-    return bf16_to_f32(static_cast<const uint16_t*>(a.src)[at]);
+    // gathered source: a chunk never straddles two ranks' parts (n / ranks is a multiple of P), so one offset per chunk
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const long at = src_offset(a, row, k * P + i);
+      float x = load_one<M>(a.src, at);
+      if constexpr (M == Mode::Finish)
+        for (int p = 1; p < a.splits; ++p) x += static_cast<const float*>(a.src)[size_t(p) * a.split_stride + at];
+      v[k] = x;
+      if (k % 4 == 3) asm volatile("" ::: "memory");
+    }
+  }
+  if constexpr (M == Mode::Prepare) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] *= a.sign[k * P + i];
+  }
+  if constexpr (M == Mode::Finish) {
+    if (a.round_z) {
+#pragma unroll
+      for (int k = 0; k < K; ++k) v[k] = bf16_to_f32(f32_to_bf16(v[k]));
+    }
   }
 }
 template <Mode M>
@@ -109,18 +142,62 @@ __device__ __forceinline__ void store_dst(const HadArgs& a, long row, int j, flo
   }
 }
 
-// Natural-order FWHT on `count` contiguous chunks of P floats in shared memory. All threads of the CTA take part.
+// Natural-order FWHT on `count` contiguous chunks of P floats in shared memory (any power-of-two P). All threads of the
+// CTA take part. Used for chunk lengths the register path below does not cover.
 __device__ __forceinline__ void fwht_shared(float* a, int P, int count) {
   const int half = (P * count) >> 1;
-  for (int h = 1; h < P; h <<= 1) {
+  int lg = 0;
+  for (int h = 1; h < P; h <<= 1, ++lg) {
     for (int t = threadIdx.x; t < half; t += blockDim.x) {
-      const int i = ((t / h) * (2 * h)) + (t % h);  // chunks are multiples of 2h, so this never straddles two chunks
+      const int i = ((t >> lg) << (lg + 1)) | (t & (h - 1));  // chunks are multiples of 2h: never straddles two chunks
       const float v = a[i], w = a[i + h];
       a[i] = v + w;
       a[i + h] = v - w;
     }
     __syncthreads();
   }
+}
+
+// Natural-order FWHT of one chunk of P = 1024 R floats held in registers by a 1,024-thread CTA: v[r] is element
+// tid + 1024 r. Index bits 0..4 are butterflied with warp shuffles; bits 5..9 after an in-place transpose through `buf`
+// (1,024 floats of shared memory, XOR-swizzled so that both the row-wise and the column-wise access are
+// bank-conflict-free), again with shuffles; bits 10 and up are between the registers of one thread. Same stage order
+// (h = 1, 2, 4, ...) and therefore the same bits as fwht_shared.
+template <int R>
+__device__ __forceinline__ void fwht_regs(float (&v)[R], float* buf) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1) {
+      const float p = __shfl_xor_sync(0xffffffffu, v[r], h);
+      v[r] = (lane & h) ? p - v[r] : v[r] + p;
+    }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    __syncthreads();  // buf is free: every thread holds its elements in registers
+    buf[warp * 32 + (lane ^ warp)] = v[r];
+    __syncthreads();
+    float t = buf[lane * 32 + (warp ^ lane)];  // element (lane << 5) | warp: lane now indexes bits 5..9
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1) {
+      const float p = __shfl_xor_sync(0xffffffffu, t, h);
+      t = (lane & h) ? p - t : t + p;
+    }
+    __syncthreads();
+    buf[lane * 32 + (warp ^ lane)] = t;
+    __syncthreads();
+    v[r] = buf[warp * 32 + (lane ^ warp)];
+  }
+#pragma unroll
+  for (int h = 1; h < R; h <<= 1)
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if ((r & h) == 0) {
+        const float x = v[r], y = v[r + h];
+        v[r] = x + y;
+        v[r + h] = x - y;
+      }
 }
 
 // Mixed value of chunk r at column i: sum over k (ascending) of +-v[k].
@@ -132,30 +209,65 @@ __device__ __forceinline__ float mix_row(const float (&v)[K], uint32_t mask) {
   return s;
 }
 
+// FWHT of the K chunks of a mixed row in shared memory, results straight to the destination.
+template <int R, Mode M>
+__device__ __forceinline__ void row_chunks_regs(const HadArgs& a, long row, float* row_s, int K) {
+  const int P = 1024 * R;
+  for (int c = 0; c < K; ++c) {
+    float v[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) v[r] = row_s[c * P + threadIdx.x + 1024 * r];
+    fwht_regs<R>(v, row_s + c * P);  // the chunk's own storage is the transpose buffer
+#pragma unroll
+    for (int r = 0; r < R; ++r) store_dst<M>(a, row, c * P + threadIdx.x + 1024 * r, v[r]);
+  }
+}
+
 template <int K, bool T, Mode M>
-__global__ __launch_bounds__(1024) void had_row_kernel(HadArgs a) {
+__global__ __launch_bounds__(1024, 1) void had_row_kernel(HadArgs a) {
   extern __shared__ float row_s[];
   constexpr SignMasks<K, T> masks{};
   const long row = blockIdx.x;
   const int P = a.P;
   if constexpr (K == 1) {
-    for (int i = threadIdx.x; i < P; i += blockDim.x) row_s[i] = load_src<M>(a, row, i);
+    for (int i = threadIdx.x; i < P; i += blockDim.x) {
+      float v[1];
+      load_column<1, M>(a, row, i, P, v);
+      row_s[i] = v[0];
+    }
   } else {
     for (int i = threadIdx.x; i < P; i += blockDim.x) {
       float v[K];
-#pragma unroll
-      for (int k = 0; k < K; ++k) v[k] = load_src<M>(a, row, k * P + i);
+      load_column<K, M>(a, row, i, P, v);
 #pragma unroll
       for (int r = 0; r < K; ++r) row_s[r * P + i] = mix_row<K>(v, masks.m[r]);
     }
   }
   __syncthreads();
+  if (P == 1024) return row_chunks_regs<1, M>(a, row, row_s, K);
+  if (P == 2048) return row_chunks_regs<2, M>(a, row, row_s, K);
   fwht_shared(row_s, P, K);
   for (int j = threadIdx.x; j < a.n; j += blockDim.x) store_dst<M>(a, row, j, row_s[j]);
 }
 
+template <int K, int R, Mode M>
+__device__ __forceinline__ void chunk_regs(const HadArgs& a, long row, int r_out, uint32_t mask, float* buf) {
+  const int P = 1024 * R;
+  float w[R];
+#pragma unroll
+  for (int q = 0; q < R; ++q) {
+    const int i = threadIdx.x + 1024 * q;
+    float v[K];
+    load_column<K, M>(a, row, i, P, v);
+    w[q] = mix_row<K>(v, mask);
+  }
+  fwht_regs<R>(w, buf);
+#pragma unroll
+  for (int q = 0; q < R; ++q) store_dst<M>(a, row, r_out * P + threadIdx.x + 1024 * q, w[q]);
+}
+
 template <int K, bool T, Mode M>
-__global__ __launch_bounds__(1024) void had_chunk_kernel(HadArgs a) {
+__global__ __launch_bounds__(1024, 1) void had_chunk_kernel(HadArgs a) {
   extern __shared__ float row_s[];
   constexpr SignMasks<K, T> masks{};
   const int r = blockIdx.x;
@@ -165,10 +277,11 @@ __global__ __launch_bounds__(1024) void had_chunk_kernel(HadArgs a) {
 #pragma unroll
   for (int q = 0; q < K; ++q)
     if (q == r) mask = masks.m[q];
+  if (P == 1024 && blockDim.x == 1024) return chunk_regs<K, 1, M>(a, row, r, mask, row_s);
+  if (P == 2048 && blockDim.x == 1024) return chunk_regs<K, 2, M>(a, row, r, mask, row_s);
   for (int i = threadIdx.x; i < P; i += blockDim.x) {
     float v[K];
-#pragma unroll
-    for (int k = 0; k < K; ++k) v[k] = load_src<M>(a, row, k * P + i);
+    load_column<K, M>(a, row, i, P, v);
     row_s[i] = mix_row<K>(v, mask);
   }
   __syncthreads();
