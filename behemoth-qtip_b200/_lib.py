@@ -47,6 +47,7 @@ SIGNATURES = {
     "qtip_k_diff_split_bf16": [_P, _P, _L, _L, _L, _P, _P, _L, _P],
     "qtip_quantize_tiles": [_P, _I, _P, _P, _P, _P, _Z, _P],
     "qtip_quantize_tiles_scatter": [_P, _I, _I, _P, _P, _I, _I, _P, _L, _I, _P, _Z, _P],
+    "qtip_quantize_tiles_noalloc": [_P, _I, _P, _P, _P, _P],
     "qtip_workspace_status": [_P, _P],
     "qtip_k_viterbi_fwd_words": [_P, _P, _I, _I, _P, _I, _P, _P, _P, _P],
     "qtip_k_viterbi_overlap_words": [_P, _P, _I, _P, _P],

@@ -17,6 +17,8 @@
 //    the other half's minima are in flight. Back-pointers go to global memory as one 32-bit word per (8 steps, group).
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -676,6 +678,45 @@ extern "C" int qtip_quantize_tiles_scatter(const float* X_d, int B, int b0, cons
   return quantize_tiles_impl(X_d, B, b0, lut_h2_d, Q_d, nblk, blk, nullptr, hatWT_d, m, col0, workspace_d,
                              workspace_bytes, true, as_stream(stream));
 }
+// ---- allocation-free variant of qtip_quantize_tiles
+// Some hosts of this library may not allocate device memory at all: a serving process whose memory pool is sized once at
+// start-up and frozen, a plugin that is handed a fixed arena by its framework, or a latency-critical loop in which
+// cudaMalloc is banned because it synchronises the whole device and can fail once memory is fragmented. For them the
+// Viterbi scratch (status word, final states, overlaps, back-pointer words) lives in the array below, which is part of
+// the loaded module: every GPU that loads the library holds these 16 MiB until the process exits.
+constexpr int kNoAllocMaxTiles = 64;
+constexpr size_t kNoAllocBytes = kWsHeader + 256 + 256 + size_t(kNoAllocMaxTiles) * kBpBytes;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+static std::mutex g_noalloc_mu;
+static void* g_noalloc_ptr[64];  // device address of the array on each device, resolved on first use
+
+extern "C" int qtip_quantize_tiles_noalloc(const float* X_d, int B, const uint32_t* lut_h2_d, uint16_t* states_d,
+                                           float* hat_d, void* stream) {
+  if (B == 0) return QTIP_OK;
+  QB_REQUIRE(X_d && lut_h2_d && B > 0, QTIP_E_ARG, "qtip_quantize_tiles_noalloc: bad argument");
+  QB_REQUIRE(B <= kNoAllocMaxTiles, QTIP_E_WORKSPACE,
+             "qtip_quantize_tiles_noalloc: %d sequences exceed the built-in scratch of %d; split the batch or use "
+             "qtip_quantize_tiles with a caller-owned workspace", B, kNoAllocMaxTiles);
+  if (!device_info()) return QTIP_E_DEVICE;
+  int dev = 0;
+  QB_CUDA(cudaGetDevice(&dev));
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+      // In host code the array's name is only a handle; the kernels need its address on the current device.
+      void* p = nullptr;
+      QB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+      g_noalloc_ptr[dev] = p;
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  // The array keeps whatever the previous call left: the status word is cleared by the shared body (reset_status),
+  // every other field is written before it is read.
+  return quantize_tiles_impl(X_d, B, 0, lut_h2_d, states_d, 1, 0, hat_d, nullptr, 0, 0, scratch, kNoAllocBytes, true,
+                             as_stream(stream));
+}
+
 extern "C" int qtip_workspace_status(const void* workspace_d, void* stream) {
   QB_REQUIRE(workspace_d, QTIP_E_ARG, "qtip_workspace_status: null workspace");
   int st = 0;

@@ -103,6 +103,17 @@ int qtip_quantize_tiles_scatter(const float* X_d, int B, int b0, const uint32_t*
                                 int blk, float* hatWT_d, long m, int col0, void* workspace_d, size_t workspace_bytes,
                                 void* stream);
 
+/* qtip_quantize_tiles for callers that must not allocate device memory (a process with a frozen memory pool, a plugin
+ * working inside an arena it was given, a loop where cudaMalloc's device-wide synchronisation is not acceptable): the
+ * scratch is a 16 MiB array inside the library's device module, so no workspace is passed and nothing is allocated,
+ * here or by the caller. Limit: B <= 64 sequences per call (QTIP_E_WORKSPACE above that; split the batch). Outputs are
+ * bit-identical to qtip_quantize_tiles. The first call on a device looks the array's device address up
+ * (cudaGetSymbolAddress): make that first call outside any stream capture, with the device current. All calls on a
+ * device share the one array, so two calls whose kernels can overlap on the GPU (different streams) race; calls on
+ * one stream are safe. This entry point has no counterpart in the reference. */
+int qtip_quantize_tiles_noalloc(const float* X_d, int B, const uint32_t* lut_h2_d, uint16_t* states_d, float* hat_d,
+                                void* stream);
+
 /* Synchronises `stream`, then returns QTIP_E_KERNEL if a fused call that used this workspace since its last reset
  * reported a timed-out hand-shake between thread blocks (its outputs are then invalid), else QTIP_OK. Each fused call
  * resets the status word when it starts. The reference has no counterpart: its kernels have no inter-block waits. */
