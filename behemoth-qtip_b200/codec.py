@@ -269,3 +269,67 @@ def unswizzle_for_kernel(words, m, n, out=None):
         out = torch.empty_like(words)
     lib().call("qtip_unswizzle_for_kernel", _p(words, torch.int16), m, n, _p(out, torch.int16), _stream())
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# quantize_group of the reference (src/quantizer.cpp:124-346) assembled from the kernels above: Hessian rotation,
+# weight rotation and scaling, LDLQ + Viterbi, proxy error, pack + kernel layout. The block LDL itself is an input
+# (`L`, strictly block-lower fp32): the reference computes it on the CPU in fp64 (src/qtip_core.cpp:444-487).
+
+def rotate_hessian(H, su, sigma_reg=1e-2):
+    """HRr = hadUt(hadUt((H + creg I) scaled by SU on both sides)^T) for H [n, n] f32 on the device (modified in place
+    and returned rotated); returns (HRr, creg). src/quantizer.cpp:124-152."""
+    init()
+    n = H.shape[0]
+    acc = torch.zeros(1, dtype=torch.float64, device=H.device)
+    k_diag_sum(H, n, acc)
+    creg = sigma_reg * float(acc) / n
+    k_add_diag(H, n, creg)
+    k_scale_rows_cols(H, n, n, n, su, su)
+    k_hadamard_rows(H, n, n, n, True)
+    HR = torch.empty_like(H)
+    k_transpose(H, n, n, n, HR, n)
+    k_hadamard_rows(HR, n, n, n, True)
+    return HR, creg
+
+
+def rotate_weight(W, su, sv, lut_rms, scale_override=0.9):
+    """WT [n, m] = (T_m^T diag(SV) W diag(SU) T_n)^T / Wscale with Wscale = rms / (float32(lut_rms) * scale_override).
+    W [m, n] f32 on the device (scratch: overwritten). Returns (WT, wscale). src/quantizer.cpp:236-250."""
+    init()
+    m, n = W.shape
+    k_scale_rows_cols(W, m, n, n, sv, su)
+    k_hadamard_rows(W, m, n, n, True)
+    WT = torch.empty((n, m), dtype=torch.float32, device=W.device)
+    k_transpose(W, m, n, n, WT, m)
+    k_hadamard_rows(WT, n, m, m, True)
+    acc = torch.zeros(1, dtype=torch.float64, device=W.device)
+    k_sumsq(WT, n, m, m, acc)
+    rms = (float(acc) / (float(n) * m)) ** 0.5
+    wscale = float(np.float32(rms / (float(np.float32(lut_rms)) * scale_override)))
+    k_scale(WT, n, m, m, 1.0 / wscale)
+    return WT, wscale
+
+
+def proxy_error(WT, hatWT, HRr):
+    """tr(D H D^T) / tr(W H W^T) in the rotated, scaled domain (D = W - hatW), fp32 GEMMs with fp64 reduction.
+    src/quantizer.cpp:272-301 (the reference uses split-bf16 GEMMs for the same traces)."""
+    D = WT - hatWT
+    num = (D * (HRr @ D)).sum(dtype=torch.float64)
+    den = (WT * (HRr @ WT)).sum(dtype=torch.float64)
+    return float(num / den)
+
+
+def quantize_linear(W, L, su, sv, lut_h2, lut_rms, workspace=None, scale_override=0.9):
+    """One linear of a Hessian group: rotate, scale, LDLQ + Viterbi, pack, kernel layout.
+    W [m, n] f32 (device, overwritten), L [n, n] f32 strictly block-lower. Returns a dict with the checkpoint tensors
+    (trellis int16 [(m/16)(n/16), 32] in kernel layout, SU bf16, SV f32 = sign * Wscale) plus WT, hatWT, Q."""
+    m, n = W.shape
+    WT, wscale = rotate_weight(W, su, sv, lut_rms, scale_override)
+    hatWT = torch.empty_like(WT)
+    Q = torch.empty(((m // 16) * (n // 16), 128), dtype=torch.int16, device=W.device)
+    ws = ldlq_gpu(WT, L, n, m, hatWT, Q, lut_h2, workspace=workspace)
+    packed = pack_trellis(Q)
+    trellis = swizzle_for_kernel(packed, m, n)
+    return {"trellis": trellis, "SU": su.to(torch.bfloat16), "SV": sv * wscale, "wscale": wscale, "WT": WT,
+            "hatWT": hatWT, "Q": Q, "workspace": ws}

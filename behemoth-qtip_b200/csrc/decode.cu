@@ -280,8 +280,10 @@ int decode_device_setup(DeviceInfo*) {
   return QTIP_OK;
 }
 
-static int check_matrix(const qtip_matrix& w, const char* who) {
-  QB_REQUIRE(w.trellis && w.lut, QTIP_E_ARG, "%s: null trellis or lut", who);
+// need_codes: the multiply and decode entry points read the trellis and the LUT; the two transforms only need the
+// geometry and SU / SV (a tensor-parallel rank runs the output transform on the full width but holds a shard of codes).
+static int check_matrix(const qtip_matrix& w, const char* who, bool need_codes = true) {
+  QB_REQUIRE(!need_codes || (w.trellis && w.lut), QTIP_E_ARG, "%s: null trellis or lut", who);
   QB_REQUIRE(w.in > 0 && w.out > 0 && w.in % 32 == 0 && w.out % 32 == 0, QTIP_E_GEOMETRY,
              "%s: in = %d, out = %d must be positive multiples of 32", who, w.in, w.out);
   return QTIP_OK;
@@ -317,7 +319,7 @@ using namespace qb;
 extern "C" int qtip_prepare(qtip_matrix w, const uint16_t* x_d, float* scratch_d, uint16_t* rotated_d, void* stream,
                             int tokens, int rank_major) {
   (void)scratch_d;  // the transforms keep their intermediate on chip
-  int rc = check_matrix(w, "qtip_prepare");
+  int rc = check_matrix(w, "qtip_prepare", false);
   if (rc) return rc;
   QB_REQUIRE(x_d && rotated_d && w.su && tokens >= 1, QTIP_E_ARG, "qtip_prepare: bad argument");
   if (!device_info()) return QTIP_E_DEVICE;
@@ -336,7 +338,7 @@ extern "C" int qtip_multiply(qtip_matrix w, const uint16_t* rotated_d, float* z_
 extern "C" int qtip_finish(qtip_matrix w, const float* z_d, uint16_t* y_d, float* scratch_d, int round_z, int splits,
                            void* stream, int tokens, int rank_major) {
   (void)scratch_d;
-  int rc = check_matrix(w, "qtip_finish");
+  int rc = check_matrix(w, "qtip_finish", false);
   if (rc) return rc;
   QB_REQUIRE(z_d && y_d && w.sv && tokens >= 1, QTIP_E_ARG, "qtip_finish: bad argument");
   QB_REQUIRE(splits >= 1 && splits <= 32, QTIP_E_GEOMETRY, "qtip_finish: splits = %d", splits);
@@ -348,7 +350,7 @@ extern "C" int qtip_finish(qtip_matrix w, const float* z_d, uint16_t* y_d, float
 extern "C" int qtip_finish_b16(qtip_matrix w, const uint16_t* z_d, uint16_t* y_d, float* scratch_d, int tokens,
                                void* stream, int rank_major) {
   (void)scratch_d;
-  int rc = check_matrix(w, "qtip_finish_b16");
+  int rc = check_matrix(w, "qtip_finish_b16", false);
   if (rc) return rc;
   QB_REQUIRE(z_d && y_d && w.sv && tokens >= 1, QTIP_E_ARG, "qtip_finish_b16: bad argument");
   if (!device_info()) return QTIP_E_DEVICE;

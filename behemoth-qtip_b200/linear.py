@@ -23,18 +23,21 @@ class Matrix:
     """Owns the device tensors of one linear and exposes the POD QtipMatrix the C ABI takes by value."""
 
     def __init__(self, trellis, su, sv, lut, n_in, n_out):
-        assert trellis.dtype == torch.int16 and trellis.numel() == (n_out // 16) * (n_in // 16) * 32
+        # trellis may be None for an object that is only handed to the transforms (qtip_prepare / qtip_finish)
+        assert trellis is None or (trellis.dtype == torch.int16 and
+                                   trellis.numel() == (n_out // 16) * (n_in // 16) * 32)
         assert su.dtype == torch.float32 and su.numel() == n_in and sv.dtype == torch.float32 and sv.numel() == n_out
         self.trellis, self.su, self.sv, self.lut, self.n_in, self.n_out = trellis, su, sv, lut, n_in, n_out
 
     @property
     def pod(self):
-        return QtipMatrix(self.trellis.data_ptr(), self.su.data_ptr(), self.sv.data_ptr(), self.lut.data_ptr(),
-                          self.n_in, self.n_out)
+        return QtipMatrix(None if self.trellis is None else self.trellis.data_ptr(), self.su.data_ptr(),
+                          self.sv.data_ptr(), None if self.lut is None else self.lut.data_ptr(), self.n_in, self.n_out)
 
     def rows(self, row0, rows):
         """Matrix of output rows [row0, row0 + rows) (whole 32-row block-rows): a contiguous run of the trellis, the
-        sharding unit of rotated-row tensor parallelism. SV is kept whole: the output transform runs on full rows."""
+        sharding unit of rotated-row tensor parallelism. Use it for qtip_multiply only: the output transform runs on the
+        gathered full-width z with the full matrix's SV."""
         assert row0 % 32 == 0 and rows % 32 == 0
         per = (self.n_in // 32) * 128
         t = self.trellis.view(-1)[(row0 // 32) * per:((row0 + rows) // 32) * per]

@@ -240,6 +240,14 @@ def main():
     achieved = lane_ops / (kern_ms * 1e-3)
     launches_per_step = 4 * ((tiles_local + chunk - 1) // chunk)
 
+    gemv = None
+    if not args.no_extras:
+        try:
+            gemv = gemv_section(pkg, peaks, peak_src, rank, world)
+        except Exception as ex:  # the headline line must survive a failure of the secondary section
+            if world > 1:
+                raise
+            gemv = {"error": repr(ex)}
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -293,10 +301,7 @@ def main():
                          "frac_at_sampled_clock": (achieved / (sm_count * 128 * clocks["sm_mhz"] * 1e6)
                                                    if clocks and clocks.get("sm_mhz") else None)}}
     if not args.no_extras:
-        try:
-            line["gemv"] = gemv_section(pkg, peaks, peak_src)
-        except Exception as ex:  # the headline line must survive a failure of the secondary section
-            line["gemv"] = {"error": repr(ex)}
+        line["gemv"] = gemv
         Xs = synth.tile_sequences(synth.gaussian_matrix(256, 4096 * 16, 2))
         line["cpu_baseline"] = cpu_reference_rate(12.0, Xs, tl.view(np.uint16))
     print(json.dumps(line))
@@ -305,53 +310,94 @@ def main():
         dist.destroy_process_group()
 
 
-def gemv_section(pkg, peaks, peak_src):
-    """Batch-1 trellis-decode GEMV y = W x for a 57344 x 12288 2-bit weight: multiply kernel alone and the whole
-    operator (input transform + multiply + output transform), as achieved HBM GB/s on the algorithmic bytes."""
+def _time_us(fn, iters, torch):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+def _graph_us(fn, reps, torch):
+    """GPU time of one fn() with the launches replayed from a CUDA graph (no host launch overhead in the number)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(reps):
+            fn()
+    return _time_us(g.replay, 5, torch) / reps
+
+
+def gemv_section(pkg, peaks, peak_src, rank, world):
+    """Batch-1 trellis-decode GEMV y = W x for a 57344 x 12288 2-bit weight. One GPU: the multiply kernel alone and the
+    whole operator (input transform + multiply + output transform), as achieved HBM GB/s on the algorithmic bytes.
+    N GPUs: rotated-row tensor parallelism, each rank multiplies its contiguous block-rows, NCCL all-gather of z,
+    output transform on every rank; time = max over ranks."""
     import torch
+    import torch.distributed as dist
     linear, synth = pkg.linear, pkg.synth
     n_in, n_out = 12288, 57344
+    row0, rows = pkg.sharding.block_row_range(n_out, rank, world)
     g = torch.Generator(device="cuda")
-    g.manual_seed(9)
-    trellis = torch.randint(-32768, 32768, ((n_out // 16) * (n_in // 16) * 32,), generator=g, device="cuda",
+    g.manual_seed(9 + rank)
+    trellis = torch.randint(-32768, 32768, ((rows // 16) * (n_in // 16) * 32,), generator=g, device="cuda",
                             dtype=torch.int16)
     su = torch.from_numpy(synth.signs(n_in, 7)).cuda()
     sv = torch.from_numpy(synth.signs(n_out, 8)).cuda()
-    w = linear.Matrix(trellis, su, sv, linear.runtime_lut(synth.seeded_tlut(1)), n_in, n_out)
+    lut = linear.runtime_lut(synth.seeded_tlut(1))
+    shard = linear.Matrix(trellis, su, sv[row0:row0 + rows].contiguous(), lut, n_in, rows)
+    g.manual_seed(10)
     x = torch.randn(n_in, generator=g, device="cuda").to(torch.bfloat16)
     y = torch.empty(n_out, dtype=torch.bfloat16, device="cuda")
     rot = torch.empty(n_in, dtype=torch.bfloat16, device="cuda")
     scratch = torch.empty(n_out, dtype=torch.float32, device="cuda")
     algo_bytes = n_out * n_in // 4 + 2 * n_in + 4 * n_out + 4096
-    res = {"algorithmic_bytes": algo_bytes, "peak_gbs": peaks["hbm_gbs"], "peak_source": peak_src}
-    best = None
-    for splits in (1, 2, 3, 4):
-        z = torch.empty((splits, n_out), dtype=torch.float32, device="cuda")
-        linear.qtip_prepare(w, x, scratch, rot)
-        for _ in range(3):
-            linear.qtip_multiply(w, rot, z, n_out, splits)
-        torch.cuda.synchronize()
-        iters = 20
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):  # 176 MB of codes per call exceed the L2, so no flush is needed between calls
-            linear.qtip_multiply(w, rot, z, n_out, splits)
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / iters
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record()
-        for _ in range(iters):
-            linear.qtip_forward(w, x, y, scratch, rot, z, False, splits)
-        f1.record()
-        torch.cuda.synchronize()
-        fus = f0.elapsed_time(f1) * 1e3 / iters
-        res["splits_%d" % splits] = {"multiply_us": us, "forward_us": fus}
-        if best is None or us < best[1]:
-            best = (splits, us, fus)
-    res.update({"best_splits": best[0], "multiply_us": best[1], "forward_us": best[2],
-                "multiply_gbs": algo_bytes / best[1] / 1e3, "forward_gbs": algo_bytes / best[2] / 1e3,
-                "multiply_frac_of_peak": algo_bytes / best[1] / 1e3 / peaks["hbm_gbs"]})
+    res = {"algorithmic_bytes": algo_bytes, "peak_gbs": peaks["hbm_gbs"], "peak_source": peak_src, "n_gpus": world,
+           "timing": "CUDA events; 176 MB of codes per call exceed the L2, so no flush between calls"}
+    if world == 1:
+        best = None
+        for splits in (1, 2, 3, 4):
+            z = torch.empty((splits, n_out), dtype=torch.float32, device="cuda")
+            linear.qtip_prepare(shard, x, scratch, rot)
+            us = _time_us(lambda: linear.qtip_multiply(shard, rot, z, n_out, splits), 20, torch)
+            fus = _graph_us(lambda: linear.qtip_forward(shard, x, y, scratch, rot, z, False, splits), 10, torch)
+            res["splits_%d" % splits] = {"multiply_us": us, "forward_us": fus}
+            if best is None or fus < best[2]:
+                best = (splits, us, fus)
+        res.update({"best_splits": best[0], "multiply_us": best[1], "forward_us": best[2],
+                    "multiply_gbs": algo_bytes / best[1] / 1e3, "forward_gbs": algo_bytes / best[2] / 1e3,
+                    "multiply_frac_of_peak": algo_bytes / best[1] / 1e3 / peaks["hbm_gbs"],
+                    "forward_frac_of_peak": algo_bytes / best[2] / 1e3 / peaks["hbm_gbs"],
+                    "forward_timing": "CUDA graph replay of prepare + multiply + finish"})
+        return res
+    full = linear.Matrix(None, su, sv, None, n_in, n_out)  # the output transform needs the geometry and SV only
+    z_local = torch.empty(rows, dtype=torch.float32, device="cuda")
+    z_full = torch.empty(n_out, dtype=torch.float32, device="cuda")
+
+    def forward_tp():
+        linear.qtip_prepare(shard, x, scratch, rot)
+        linear.qtip_multiply(shard, rot, z_local, rows, 1)
+        dist.all_gather_into_tensor(z_full, z_local)
+        linear.qtip_finish(full, z_full, y, scratch, False, 1)
+
+    dist.barrier()
+    fus = _time_us(forward_tp, 50, torch)
+    mus = _time_us(lambda: linear.qtip_multiply(shard, rot, z_local, rows, 1), 50, torch)
+    t = torch.tensor([fus, mus], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    fus, mus = float(t[0]), float(t[1])
+    res.update({"forward_us": fus, "multiply_us": mus, "forward_gbs": algo_bytes / fus / 1e3,
+                "multiply_gbs": algo_bytes / mus / 1e3, "collective": "ncclAllGather of z (fp32, %d B per rank)" % (rows * 4)})
     return res
 
 

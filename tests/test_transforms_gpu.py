@@ -151,3 +151,54 @@ def test_ldlq_bit_exact_vs_restated_schedule(gpu, oracle, hyb):
     assert np.array_equal(u16(Q2)[nb:3 * nb], oQ[nb:3 * nb])
     assert np.array_equal(hat2.cpu().numpy()[:, 16:48], ohat[:, 16:48])
     assert bool((hat2[:, :16] == 7.0).all()) and bool((hat2[:, 48:] == 7.0).all())
+
+
+def test_quantize_linear_round_trip_through_the_runtime_operator(gpu, oracle):
+    """Encode side meets decode side: a 64 x 384 linear is rotated, LDLQ-quantised, packed into the checkpoint layout,
+    and the runtime operator on those tensors must reproduce y = W_hat x, where W_hat is the encoder's own
+    reconstruction diag(SV) T_m (hatWr Wscale) T_n^T diag(SU). Also: LDLQ beats plain nearest-path quantisation in the
+    Hessian-weighted proxy error, and the device rotation agrees with the fp64 transform."""
+    s = gpu.synth
+    m, n = 64, 384
+    rng = np.random.default_rng(33)
+    W = (0.02 * rng.standard_normal((m, n))).astype(np.float32)
+    H = s.spd_hessian(n, 34)
+    su, sv = s.signs(n, 7), s.signs(m, 8)
+    tl = s.seeded_tlut(1)
+    lut_d, lut_rms = gpu.codec.device_lut(tl)
+    HRr, creg = gpu.codec.rotate_hessian(dev(H.astype(np.float32)), dev(su))
+    Href = oracle.hadamard_rows(oracle.hadamard_rows((H + creg * np.eye(n)) * su[None, :] * su[:, None], True).T.copy(), True)
+    assert np.abs(HRr.cpu().numpy() - Href).max() < 2e-5 * max(1.0, np.abs(Href).max())
+    Hs = 0.5 * (Href + Href.T)
+    L = oracle.block_ldl(Hs)
+    out = gpu.codec.quantize_linear(dev(W), dev(L), dev(su), dev(sv), lut_d, lut_rms)
+    torch.cuda.synchronize()
+    WT, hatWT = out["WT"], out["hatWT"]
+    Wr_ref = oracle.hadamard_rows(oracle.hadamard_rows((W * sv[:, None] * su[None, :]).astype(np.float64), True).T.copy(), True)
+    assert np.abs(WT.cpu().numpy() * out["wscale"] - Wr_ref).max() < 2e-5
+    # proxy error: LDLQ (with feedback) vs the same quantiser without feedback (identity Hessian)
+    p_ldlq = gpu.codec.proxy_error(WT, hatWT, dev(Hs.astype(np.float32)))
+    hat0 = torch.empty_like(WT)
+    Q0 = torch.empty_like(out["Q"])
+    gpu.codec.ldlq_gpu(WT, torch.zeros((n, n), dtype=torch.float32, device="cuda"), n, m, hat0, Q0, lut_d)
+    p_plain = gpu.codec.proxy_error(WT, hat0, dev(Hs.astype(np.float32)))
+    assert p_ldlq < p_plain and p_ldlq < 0.2
+    # decode the checkpoint tensors with the oracle and compare with the encoder's hatWT (fp16 LUT values, exact)
+    tr = out["trellis"].cpu().numpy().view(np.uint16).reshape(-1)
+    dec = oracle.decode_rows(tr, n, m, tl.view(np.uint16), 0, m, False)
+    assert np.array_equal(dec, hatWT.cpu().numpy().T)
+    # runtime operator on the written tensors vs the dense reconstruction
+    w = gpu.linear.Matrix(out["trellis"].view(-1), dev(su), out["SV"].contiguous(), gpu.linear.runtime_lut(tl), n, m)
+    x = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    xb = s.f32_to_bf16_bits(x)
+    y = torch.empty(m, dtype=torch.bfloat16, device="cuda")
+    rot = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    z = torch.empty(m, dtype=torch.float32, device="cuda")
+    gpu.linear.qtip_forward(w, torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16), y,
+                            torch.empty(n, dtype=torch.float32, device="cuda"), rot, z, False, 1)
+    What = sv[:, None] * oracle.hadamard_rows(oracle.hadamard_rows(dec.astype(np.float64) * out["wscale"], False).T.copy(),
+                                              False).T * su[None, :]
+    y_ref = What @ s.bf16_bits_to_f32(xb).astype(np.float64)
+    err = np.linalg.norm(y.float().cpu().numpy() - y_ref) / np.linalg.norm(y_ref)
+    assert err < 2e-2, err  # bf16 LUT, bf16 rotated input and bf16 output against an fp64 dense product
+    assert np.linalg.norm(What - W) / np.linalg.norm(W) < 0.5  # 2 bits per weight: the reconstruction is W-like
