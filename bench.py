@@ -92,6 +92,11 @@ def cpu_reference_rate(seconds_target, X, tlut_bits):
     from oracle.oracle import Oracle, Reference
     R = Reference()
     threads = len(os.sched_getaffinity(0))
+    try:  # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core
+        import ctypes
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(threads)
+    except OSError:
+        pass
     x16 = lambda a: a.astype(np.float16).astype(np.float32)  # noqa: E731  (the quantizer hands the CPU path fp16 values)
     if R.available and np.array_equal(R.codebook()[0].reshape(-1), tlut_bits.reshape(-1)):
         run, kind = (lambda a: R.quantize_seqs(a)), "reference"
@@ -153,9 +158,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=M, help="rows of the matrix (default: the full 12288)")
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMV section and the CPU baseline")
+    ap.add_argument("--workload", default="viterbi", choices=["viterbi", "ldlq"],
+                    help="viterbi: the headline identity-Hessian encode; ldlq: LDLQ + Viterbi on a 12288 x 28672 matrix "
+                         "with a synthetic correlated Hessian (secondary line)")
+    ap.add_argument("--ldlq-shape", default="12288x28672", help="m x n of the ldlq workload")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.workload == "ldlq":
+        return ldlq_workload(args)
 
     import torch
     import torch.distributed as dist
@@ -302,9 +313,133 @@ def main():
                                                    if clocks and clocks.get("sm_mhz") else None)}}
     if not args.no_extras:
         line["gemv"] = gemv
+    if not args.no_extras and world == 1:
         Xs = synth.tile_sequences(synth.gaussian_matrix(256, 4096 * 16, 2))
         line["cpu_baseline"] = cpu_reference_rate(12.0, Xs, tl.view(np.uint16))
     print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def synthetic_block_ldl(n, torch, tokens=65536, rank_r=64, chunk=8192):
+    """Strictly block-lower fp32 L of the rotated, damped Hessian of synthetic activations: X = Z + Zr C (Z, Zr N(0,1),
+    C = N(0,1)/8, rank 64) in bf16, H = X^T X / tokens with fp32 accumulation, + 1e-2 mean(diag) I, two-sided
+    hadUt with seeded SU signs (this library's kernels), fp64 Cholesky and 16 x 16 block LDL (torch, on the GPU: the
+    reference does this step on the CPU in fp64). Returns (L, su)."""
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    codec, synth = pkg.codec, pkg.synth
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4)
+    C = torch.randn(rank_r, n, generator=g, device="cuda") / 8.0
+    H = torch.zeros((n, n), dtype=torch.float32, device="cuda")
+    for _ in range(0, tokens, chunk):
+        Xc = (torch.randn(chunk, n, generator=g, device="cuda") +
+              torch.randn(chunk, rank_r, generator=g, device="cuda") @ C).to(torch.bfloat16).float()
+        H.addmm_(Xc.T, Xc)
+        del Xc
+    H /= tokens
+    su = torch.from_numpy(synth.signs(n, 7)).cuda()
+    HR, creg = codec.rotate_hessian(H, su)
+    del H
+    A = HR.double()
+    del HR
+    A = 0.5 * (A + A.T)
+    Cl = torch.linalg.cholesky(A)
+    del A
+    nb = n // 16
+    D = torch.stack([Cl[16 * b:16 * b + 16, 16 * b:16 * b + 16] for b in range(nb)])      # [nb, 16, 16]
+    cols = Cl.view(n, nb, 16).permute(1, 0, 2).contiguous()                                 # [nb, n, 16]
+    del Cl
+    Lb = torch.linalg.solve_triangular(D, cols, upper=False, left=False)                    # X D = cols
+    del cols, D
+    L = Lb.permute(1, 0, 2).reshape(n, n).float()
+    del Lb
+    rb = torch.arange(n, device="cuda") // 16
+    L.masked_fill_(rb[:, None] <= rb[None, :], 0.0)  # zero the diagonal blocks and everything above
+    return L.contiguous(), su
+
+
+def ldlq_workload(args):
+    """LDLQ + Viterbi of a down_proj-shaped matrix: weights N(0, 0.02), synthetic correlated Hessian, random-Hadamard
+    rotation, 128-column buffers. Timed region: qtip_ldlq only (rotation and LDL reported beside it). Rows of W are
+    split over the ranks (no collective); every rank builds the same L."""
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    codec, synth = pkg.codec, pkg.synth
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    codec.init()
+    m, n = (int(v) for v in args.ldlq_shape.split("x"))
+    t0 = time.perf_counter()
+    L, su = synthetic_block_ldl(n, torch)
+    torch.cuda.synchronize()
+    t_ldl = time.perf_counter() - t0
+    lut_d, lut_rms = codec.device_lut(synth.seeded_tlut(1))
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    W = torch.randn(m, n, generator=g, device="cuda") * 0.02
+    sv = torch.from_numpy(synth.signs(m, 8)).cuda()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    WT_full, wscale = codec.rotate_weight(W, su, sv, lut_rms)
+    e1.record()
+    torch.cuda.synchronize()
+    t_rht = e0.elapsed_time(e1)
+    del W
+    b, e = pkg.sharding.tile_row_range(m // 16, rank, world)
+    mj = (e - b) * 16
+    WT = WT_full[:, 16 * b:16 * e].contiguous()
+    del WT_full
+    hatWT = torch.empty_like(WT)
+    Q = torch.empty(((mj // 16) * (n // 16), 128), dtype=torch.int16, device="cuda")
+    ws = codec.ldlq_workspace(n, mj)
+    times = []
+    for i in range(args.warmup + args.steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        codec.ldlq_gpu(WT, L, n, mj, hatWT, Q, lut_d, workspace=ws)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= args.warmup:
+            times.append(e0.elapsed_time(e1))
+    ws.check()
+    t = torch.tensor([sum(times) / len(times)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t)
+    # invariants on this rank's codes: trellis links, tail-biting, decode(states) == hatWT tile by tile
+    sd = Q.to(torch.int32) & 0xFFFF
+    links = bool((((sd[:, :-1] << 4) & 0xFFFF) == (sd[:, 1:] & 0xFFF0)).all()) and \
+        bool(((sd[:, 127] & 0xFFF) == (sd[:, 0] >> 4)).all())
+    nt = min(Q.shape[0], 4096)
+    dec = torch.empty((nt, 256), dtype=torch.float32, device="cuda")
+    codec.k_decode_states(Q[:nt].contiguous(), nt, dec, lut_d)
+    perm = torch.from_numpy(synth.tile_perm()).cuda()
+    nbk = n // 16
+    tiles = hatWT.T.reshape(mj // 16, 16, nbk, 16).permute(0, 2, 1, 3).reshape(-1, 256)[:nt][:, perm]
+    decode_ok = bool(torch.equal(dec, tiles))
+    D = WT - hatWT
+    rel_mse = float((D * D).sum(dtype=torch.float64) / (WT * WT).sum(dtype=torch.float64))
+    if rank == 0:
+        print(json.dumps({"metric": "ldlq_viterbi_quantized_weights_per_second", "value": m * n / (ms * 1e-3),
+                          "unit": "weights/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                          "dtype": "f32", "data": "synthetic",
+                          "config": {"workload": "ldlq_viterbi_%dx%d" % (m, n), "column_steps": n // 16,
+                                     "sequences_per_step_per_rank": mj // 16, "buffers": n // 128},
+                          "stages_ms": {"hessian_and_block_ldl_setup_s": t_ldl, "weight_rht_ms": t_rht, "ldlq_ms": ms},
+                          "checks": {"trellis_links_and_tail_biting": links, "decode_equals_hatW": decode_ok,
+                                     "relative_mse": rel_mse, "wscale": wscale}}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
