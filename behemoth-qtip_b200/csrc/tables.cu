@@ -137,6 +137,8 @@ extern "C" int qtip_init(void) {
   if (rc) return rc;
   rc = decode_device_setup(&info);
   if (rc) return rc;
+  rc = gemm_tc_device_setup();
+  if (rc) return rc;
   info.ready = true;
   g_dev[dev] = info;
   return QTIP_OK;

@@ -94,3 +94,24 @@ def reduce_to_b16(x, scale, y, elements, width, splits):
     init()
     lib().call("qtip_reduce_to_b16", _p(x, torch.float32), _p(scale, torch.float32), _p(y, torch.bfloat16), elements,
                width, splits, _stream())
+
+
+def fp8_forward(w, scale, x, y, n_in, n_out, tokens=1):
+    """FP8 e4m3 K/V projection: w uint8 [out, in], scale f32 [out], x bf16 [tokens, in] -> y bf16 [tokens, out]."""
+    init()
+    lib().call("qtip_fp8_forward", _p(w, torch.uint8), _p(scale, torch.float32), _p(x, torch.bfloat16),
+               _p(y, torch.bfloat16), n_in, n_out, tokens, _stream())
+
+
+def prefill_gemm(w_dense, x, z, stride, n_in, n_out, tokens, status=None):
+    """z [tokens, stride] f32 = x [tokens, in] . w_dense [out, in]^T on the tcgen05 tensor cores."""
+    init()
+    lib().call("qtip_prefill_gemm", _p(w_dense, torch.bfloat16), _p(x, torch.bfloat16), _p(z, torch.float32), stride,
+               n_in, n_out, tokens, _p(status, torch.int32), _stream())
+
+
+def qtip_multiply_prefill(w, x, z, stride, tokens, dense_scratch, status=None):
+    """The >= 128-token regime of the reference (Rank::multiply, runtime/cuda/tensor_model.cpp:210-222): dense bf16
+    decode of the shard into `dense_scratch` [out, in], then the tensor-core product."""
+    qtip_decode_matrix(w, dense_scratch)
+    prefill_gemm(dense_scratch, x, z, stride, w.n_in, w.n_out, tokens, status)

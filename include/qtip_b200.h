@@ -197,6 +197,20 @@ int qtip_reduce_products(float* x_d, size_t elements, int splits, void* stream);
 int qtip_reduce_to_b16(const float* x_d, const float* scale_d, uint16_t* y_d, size_t elements, int width, int splits,
                        void* stream);
 
+/* Prefill product on the tcgen05 tensor cores: z_d[token][row] (fp32, row stride `stride`) = sum_k w_dense_d[row][k] *
+ * x_d[token][k], bf16 operands (w_dense_d is the output of qtip_decode_matrix, x_d the rotated activations). Needs
+ * in % 64 == 0 and out % 128 == 0. status_d (one int, may be NULL): set to 2 if a bounded pipeline wait timed out.
+ * Replaces the cublasGemmEx call of the >= 128-token path (runtime/cuda/tensor_model.cpp:210-222). */
+int qtip_prefill_gemm(const uint16_t* w_dense_d, const uint16_t* x_d, float* z_d, int stride, int in, int out, int tokens,
+                      int* status_d, void* stream);
+
+/* FP8 (e4m3) W8A16 projection of the K/V weights kept beside the QTIP linears: y[t][o] = bf16((sum_i fp8(w[o][i]) *
+ * bf16(x[t][i])) * scale[o]), fp32 accumulation. w_d [out][in] bytes, scale_d [out], x_d [tokens][in] bf16, y_d
+ * [tokens][out] bf16. runtime/cuda/kernels.cu:279-289,477-480 (fp8_forward) and batch_kernels.cu:750-763
+ * (fp8_multiply_batch), with the token count as a parameter. */
+int qtip_fp8_forward(const uint8_t* w_d, const float* scale_d, const uint16_t* x_d, uint16_t* y_d, int in, int out,
+                     int tokens, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -157,3 +157,51 @@ def test_geometry_errors(gpu):
     assert e.value.code == -2
     with pytest.raises(gpu.QtipError):
         gpu.linear.qtip_multiply(w, u, z, 256, 33, 1)  # more than 32 splits
+
+
+@pytest.mark.parametrize("tokens", [1, 5, 19])
+def test_fp8_kv_projection(gpu, oracle, tokens):
+    """Random e4m3 bytes (NaN codes remapped to 0) with the reference test's per-row scales, against the oracle's
+    restatement of the FP8 branch of reference_forward, rounded to bf16. Tolerance: one bf16 ulp."""
+    rng = np.random.default_rng(11)
+    n_in, n_out = 1536, 200
+    w = rng.integers(0, 256, (n_out, n_in), dtype=np.uint8)
+    w[(w & 127) == 127] = 0
+    scale = ((1 + np.arange(n_out) % 7) / 4096.0).astype(np.float32)
+    xb = gpu.synth.f32_to_bf16_bits(rng.standard_normal((tokens, n_in)).astype(np.float32))
+    y = torch.empty((tokens, n_out), dtype=torch.bfloat16, device="cuda")
+    gpu.linear.fp8_forward(torch.from_numpy(w).cuda(), dev(scale), bf16_dev(xb), y, n_in, n_out, tokens)
+    ref = oracle.fp8_forward(w, scale, gpu.synth.bf16_bits_to_f32(xb), True)
+    ref_b = gpu.synth.bf16_bits_to_f32(gpu.synth.f32_to_bf16_bits(ref))
+    got = y.float().cpu().numpy()
+    assert np.abs(got - ref_b).max() <= 2.0 ** -7 * np.abs(ref_b).max()
+    assert rel_l2(got, ref_b) < 4e-3
+
+
+@pytest.mark.parametrize("n_in,n_out,tokens", [(512, 256, 300), (1024, 128, 256), (12288, 384, 17)])
+def test_prefill_gemm_tensor_cores(gpu, n_in, n_out, tokens):
+    """tcgen05 product against float64 on the same bf16 operands: fp32 accumulation, rel-L2 <= 5e-5 (K up to 12,288
+    terms per output); ragged token counts (rows past the end are not written)."""
+    rng = np.random.default_rng(n_in + tokens)
+    wb = gpu.synth.f32_to_bf16_bits(rng.standard_normal((n_out, n_in)).astype(np.float32))
+    xb = gpu.synth.f32_to_bf16_bits(rng.standard_normal((tokens, n_in)).astype(np.float32))
+    z = torch.full((tokens + 3, n_out), 7.0, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gpu.linear.prefill_gemm(bf16_dev(wb), bf16_dev(xb), z, n_out, n_in, n_out, tokens, status)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    ref = gpu.synth.bf16_bits_to_f32(xb).astype(np.float64) @ gpu.synth.bf16_bits_to_f32(wb).astype(np.float64).T
+    assert rel_l2(z[:tokens].cpu().numpy(), ref) < 5e-5
+    assert bool((z[tokens:] == 7.0).all())
+
+
+def test_multiply_prefill_matches_batch_path(gpu, oracle):
+    n_in, n_out, tokens = 1024, 256, 200
+    w, tr, su, sv, tl = make_linear(gpu, n_in, n_out, 90)
+    xb = gpu.synth.f32_to_bf16_bits(np.random.default_rng(2).standard_normal((tokens, n_in)).astype(np.float32))
+    dense = torch.empty((n_out, n_in), dtype=torch.bfloat16, device="cuda")
+    z = torch.zeros((tokens, n_out), dtype=torch.float32, device="cuda")
+    gpu.linear.qtip_multiply_prefill(w, bf16_dev(xb), z, n_out, tokens, dense)
+    W = oracle.decode_rows(tr, n_in, n_out, tl, 0, n_out, True).astype(np.float64)
+    ref = gpu.synth.bf16_bits_to_f32(xb).astype(np.float64) @ W.T
+    assert rel_l2(z.cpu().numpy(), ref) < 1e-5
