@@ -89,23 +89,34 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, int item, int nw, int
   auto process = [&](uint2 own, int blk) {
     const uint2 peer = make_uint2(__shfl_sync(0xffffffffu, own.x, (lane + 1) & 31),
                                   __shfl_sync(0xffffffffu, own.y, (lane + 1) & 31));
-    uint4 xb;
-    if constexpr (XS) xb = reinterpret_cast<const uint4*>(gemm_smem_words + c.xs_word)[blk * 4 + tg];
+    // B fragments of the block: for tile column j1 a lane needs bf16 pairs tg and tg + 4 of token g's eight pairs, i.e.
+    // words tg, tg + 4, tg + 8, tg + 12 of the block's 16 words. XS: staged in that order in shared memory. Otherwise one
+    // 16-byte load of words 4 tg .. 4 tg + 3 per token group and a 4 x 4 word transpose inside the quad (four shuffles).
+    uint32_t bw[NT][4];
+    if constexpr (XS) {
+      const uint4 xb = reinterpret_cast<const uint4*>(gemm_smem_words + c.xs_word)[blk * 4 + tg];
+      bw[0][0] = xb.x, bw[0][1] = xb.y, bw[0][2] = xb.z, bw[0][3] = xb.w;
+    } else {
+      const bool odd = tg & 1, hi = tg & 2;
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(c.xw + size_t(min(t * 8 + g, c.tokens - 1)) * c.in_words +
+                                                             blk * 16 + 4 * tg));
+        uint32_t r0 = v.x, r1 = v.y, r2 = v.z, r3 = v.w;
+        uint32_t s0 = __shfl_xor_sync(0xffffffffu, odd ? r0 : r1, 1), s1 = __shfl_xor_sync(0xffffffffu, odd ? r2 : r3, 1);
+        if (odd) r0 = s0, r2 = s1;
+        else r1 = s0, r3 = s1;
+        s0 = __shfl_xor_sync(0xffffffffu, hi ? r0 : r2, 2), s1 = __shfl_xor_sync(0xffffffffu, hi ? r1 : r3, 2);
+        if (hi) r0 = s0, r1 = s1;
+        else r2 = s0, r3 = s1;
+        bw[t][0] = r0, bw[t][1] = r1, bw[t][2] = r2, bw[t][3] = r3;
+      }
+    }
 #pragma unroll
     for (int j1 = 0; j1 < 2; ++j1) {
-      // B fragments of the 16 input columns of tile column j1: token g, columns 2 tg and 2 tg + 8
       uint32_t bf[NT][2];
-      if constexpr (XS) {
-        bf[0][0] = j1 ? xb.z : xb.x;
-        bf[0][1] = j1 ? xb.w : xb.y;
-      } else {
 #pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          const uint32_t* xr = c.xw + size_t(min(t * 8 + g, c.tokens - 1)) * c.in_words + blk * 16 + j1 * 8 + tg;
-          bf[t][0] = __ldg(xr);
-          bf[t][1] = __ldg(xr + 4);
-        }
-      }
+      for (int t = 0; t < NT; ++t) bf[t][0] = bw[t][2 * j1], bf[t][1] = bw[t][2 * j1 + 1];
       const uint32_t o = j1 ? own.y : own.x, p = j1 ? peer.y : peer.x;
 #pragma unroll
       for (int i1 = 0; i1 < 2; ++i1) {

@@ -209,17 +209,56 @@ __device__ __forceinline__ float mix_row(const float (&v)[K], uint32_t mask) {
   return s;
 }
 
-// FWHT of the K chunks of a mixed row in shared memory, results straight to the destination.
-template <int R, Mode M>
-__device__ __forceinline__ void row_chunks_regs(const HadArgs& a, long row, float* row_s, int K) {
-  const int P = 1024 * R;
-  for (int c = 0; c < K; ++c) {
-    float v[R];
+// Natural-order FWHT of 1,024 floats by ONE warp, no block-level synchronisation: v[r] is element 32 r + lane. Index
+// bits 0..4 (the lane) are butterflied with shuffles, bits 5..9 (r) between the registers of a thread. Same stage order
+// as fwht_shared / fwht_regs, therefore the same bits.
+__device__ __forceinline__ void fwht_warp_1024(float (&v)[32]) {
+  const int lane = threadIdx.x & 31;
 #pragma unroll
-    for (int r = 0; r < R; ++r) v[r] = row_s[c * P + threadIdx.x + 1024 * r];
-    fwht_regs<R>(v, row_s + c * P);  // the chunk's own storage is the transpose buffer
+  for (int h = 1; h < 32; h <<= 1) {
+    const bool upper = lane & h;
 #pragma unroll
-    for (int r = 0; r < R; ++r) store_dst<M>(a, row, c * P + threadIdx.x + 1024 * r, v[r]);
+    for (int r = 0; r < 32; ++r) {
+      const float p = __shfl_xor_sync(0xffffffffu, v[r], h);
+      v[r] = upper ? p - v[r] : v[r] + p;
+    }
+  }
+#pragma unroll
+  for (int h = 1; h < 32; h <<= 1)
+#pragma unroll
+    for (int r = 0; r < 32; ++r)
+      if ((r & h) == 0) {
+        const float x = v[r], y = v[r + h];
+        v[r] = x + y;
+        v[r + h] = x - y;
+      }
+}
+
+// FWHT of the K chunks (P = 1024 H floats each, H = 1 or 2) of a mixed row in shared memory, one 1,024-float unit per
+// warp at a time, results straight to the destination (H = 1) or after one more stage across the two halves (H = 2).
+template <int H, Mode M>
+__device__ __forceinline__ void row_chunks_warp(const HadArgs& a, long row, float* row_s, int K) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int u = warp; u < K * H; u += nwarps) {
+    float* unit = row_s + u * 1024;
+    float v[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) v[r] = unit[32 * r + lane];
+    fwht_warp_1024(v);
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+      if constexpr (H == 1) store_dst<M>(a, row, u * 1024 + 32 * r + lane, v[r]);
+      else unit[32 * r + lane] = v[r];
+    }
+  }
+  if constexpr (H == 2) {
+    __syncthreads();
+    for (int j = threadIdx.x; j < K * 1024; j += blockDim.x) {
+      const int c = j >> 10, i = j & 1023;
+      const float x = row_s[c * 2048 + i], y = row_s[c * 2048 + 1024 + i];
+      store_dst<M>(a, row, c * 2048 + i, x + y);
+      store_dst<M>(a, row, c * 2048 + 1024 + i, x - y);
+    }
   }
 }
 
@@ -244,8 +283,8 @@ __global__ __launch_bounds__(1024, 1) void had_row_kernel(HadArgs a) {
     }
   }
   __syncthreads();
-  if (P == 1024) return row_chunks_regs<1, M>(a, row, row_s, K);
-  if (P == 2048) return row_chunks_regs<2, M>(a, row, row_s, K);
+  if (P == 1024) return row_chunks_warp<1, M>(a, row, row_s, K);
+  if (P == 2048) return row_chunks_warp<2, M>(a, row, row_s, K);
   fwht_shared(row_s, P, K);
   for (int j = threadIdx.x; j < a.n; j += blockDim.x) store_dst<M>(a, row, j, row_s[j]);
 }

@@ -115,3 +115,12 @@ def qtip_multiply_prefill(w, x, z, stride, tokens, dense_scratch, status=None):
     decode of the shard into `dense_scratch` [out, in], then the tensor-core product."""
     qtip_decode_matrix(w, dense_scratch)
     prefill_gemm(dense_scratch, x, z, stride, w.n_in, w.n_out, tokens, status)
+
+
+def fp8_forward_prefill(w, scale, x, y, n_in, n_out, tokens, dense_scratch, z):
+    """FP8 K/V projection for prefill-sized batches on the tensor cores: exact bf16 copy of the weights, tcgen05 product
+    into z [tokens, out] f32, per-row scale and bf16 rounding (the reference's decode_fp8_matrix path)."""
+    init()
+    lib().call("qtip_decode_fp8_matrix", _p(w, torch.uint8), _p(dense_scratch, torch.bfloat16), n_in * n_out, _stream())
+    prefill_gemm(dense_scratch, x, z, n_out, n_in, n_out, tokens)
+    reduce_to_b16(z, scale, y, tokens * n_out, n_out, 1)

@@ -158,7 +158,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=M, help="rows of the matrix (default: the full 12288)")
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMV section and the CPU baseline")
-    ap.add_argument("--workload", default="viterbi", choices=["viterbi", "ldlq"],
+    ap.add_argument("--workload", default="viterbi", choices=["viterbi", "ldlq", "layer"],
                     help="viterbi: the headline identity-Hessian encode; ldlq: LDLQ + Viterbi on a 12288 x 28672 matrix "
                          "with a synthetic correlated Hessian (secondary line)")
     ap.add_argument("--ldlq-shape", default="12288x28672", help="m x n of the ldlq workload")
@@ -167,6 +167,8 @@ def main():
         return reference_arm(args)
     if args.workload == "ldlq":
         return ldlq_workload(args)
+    if args.workload == "layer":
+        return layer_workload(args)
 
     import torch
     import torch.distributed as dist
@@ -443,6 +445,77 @@ def ldlq_workload(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def layer_workload(args):
+    """Decode/prefill products of one Mistral-Large-shaped layer (hidden 12288, intermediate 28672, 96 Q / 8 KV heads of
+    128): q, o, gate, up, down as 2-bit QTIP linears with random codes, k, v as FP8 e4m3, bf16 activations N(0,1), token
+    batches 1, 16, 64 and 2048. Each linear runs input transform, product, output transform. <= 64 tokens: MMA-fragment
+    kernel (HBM-side metric: code bytes per second); 2048 tokens: dense decode + tcgen05 GEMM (TFLOP/s). One GPU."""
+    import torch
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    linear, synth = pkg.linear, pkg.synth
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    pkg.codec.init()
+    peaks, peak_src = measured_peaks()
+    hidden, inter, kv = 12288, 28672, 1024
+    shapes = {"q": (hidden, hidden), "o": (hidden, hidden), "gate": (hidden, inter), "up": (hidden, inter),
+              "down": (inter, hidden)}
+    lut = linear.runtime_lut(synth.seeded_tlut(1))
+    g = torch.Generator(device="cuda")
+    mats = {}
+    for i, (name, (n_in, n_out)) in enumerate(shapes.items()):
+        g.manual_seed(9 + i)
+        tr = torch.randint(-32768, 32768, ((n_out // 16) * (n_in // 16) * 32,), generator=g, device="cuda", dtype=torch.int16)
+        mats[name] = linear.Matrix(tr, torch.from_numpy(synth.signs(n_in, 7)).cuda(),
+                                   torch.from_numpy(synth.signs(n_out, 8)).cuda(), lut, n_in, n_out)
+    g.manual_seed(11)
+    w8 = [torch.randint(0, 255, (kv, hidden), generator=g, device="cuda", dtype=torch.uint8) for _ in range(2)]
+    for w in w8:
+        w[(w & 127) == 127] = 0
+    s8 = ((1 + torch.arange(kv, device="cuda") % 7) / 4096.0).float()
+    code_bytes = sum(a * b // 4 for a, b in shapes.values()) + 2 * kv * hidden
+    weights = sum(a * b for a, b in shapes.values()) + 2 * kv * hidden
+    dense = torch.empty(inter * hidden, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = {}
+    for T in (1, 16, 64, 2048):
+        g.manual_seed(10)
+        xs = {n: torch.randn(T, n, generator=g, device="cuda").to(torch.bfloat16) for n in (hidden, inter)}
+        rot = {n: torch.empty(T, n, dtype=torch.bfloat16, device="cuda") for n in (hidden, inter)}
+        ys = {n: torch.empty(T, n, dtype=torch.bfloat16, device="cuda") for n in (hidden, inter, kv)}
+        splits = {name: (2 if (T <= 64 and shapes[name][1] == hidden) else 1) for name in shapes}
+        z = torch.empty(2 * T * inter, dtype=torch.float32, device="cuda")
+        scratch = torch.empty(1, dtype=torch.float32, device="cuda")
+
+        def layer():
+            for name, (n_in, n_out) in shapes.items():
+                w, sp = mats[name], splits[name]
+                linear.qtip_prepare(w, xs[n_in], scratch, rot[n_in], T)
+                if T >= 128:
+                    linear.qtip_multiply_prefill(w, rot[n_in], z, n_out, T, dense[:n_out * n_in].view(n_out, n_in), status)
+                elif T == 1:
+                    linear.qtip_multiply(w, rot[n_in], z, n_out, sp, 1)
+                else:
+                    linear.qtip_multiply_batch(w, rot[n_in], z, n_out, sp, T)
+                linear.qtip_finish(w, z, ys[n_out], scratch, name in ("gate", "up"), sp, T)
+            for w in w8:
+                if T >= 128:
+                    linear.fp8_forward_prefill(w, s8, xs[hidden], ys[kv], hidden, kv, T, dense[:kv * hidden], z)
+                else:
+                    linear.fp8_forward(w, s8, xs[hidden], ys[kv], hidden, kv, T)
+
+        us = _graph_us(layer, 2, torch) if T <= 64 else _time_us(layer, 3, torch)
+        flops = 2.0 * T * weights
+        out["T%d" % T] = {"layer_us": us, "code_gbs": code_bytes / us / 1e3, "tflops": flops / us / 1e6,
+                          "frac_of_hbm_peak": code_bytes / us / 1e3 / peaks["hbm_gbs"],
+                          "frac_of_bf16_peak": flops / us / 1e6 / peaks["bf16_tflops"]}
+        del xs, rot, ys, z
+    assert int(status) == 0
+    print(json.dumps({"metric": "qtip_layer_products", "unit": "us per layer", "n_gpus": 1, "data": "synthetic",
+                      "config": {"workload": "mistral_large_layer_products", "hidden": hidden, "intermediate": inter,
+                                 "code_bytes": code_bytes, "weights": weights, "peaks": peak_src}, "tokens": out}))
 
 
 def _time_us(fn, iters, torch):

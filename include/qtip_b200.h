@@ -211,6 +211,10 @@ int qtip_prefill_gemm(const uint16_t* w_dense_d, const uint16_t* x_d, float* z_d
 int qtip_fp8_forward(const uint8_t* w_d, const float* scale_d, const uint16_t* x_d, uint16_t* y_d, int in, int out,
                      int tokens, void* stream);
 
+/* Exact bf16 copy of an e4m3 weight matrix for the prefill product (then qtip_prefill_gemm and qtip_reduce_to_b16 with
+ * the per-row scale). runtime/cuda/batch_kernels.cu:694-698,845-848 (decode_fp8_matrix). */
+int qtip_decode_fp8_matrix(const uint8_t* w_d, uint16_t* out_d, size_t elements, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
