@@ -1,14 +1,19 @@
 // Prefill-sized products on the 5th-generation tensor cores: z[token][row] = sum_k W[row][k] x[token][k], bf16 operands,
-// fp32 accumulation in tensor memory (tcgen05.mma, cta_group::1, M = 128 weight rows x N = 256 tokens x K = 64 per stage).
+// fp32 accumulation in tensor memory (tcgen05.mma, cta_group::1, M = 128 x N = 256 x K = 16 per instruction). A CTA owns a
+// 256 (weight rows) x 256 (tokens) output tile as two 128-row accumulators that share the token tile: 64 KiB of operands
+// per 64-deep stage feed 8.4 MFLOP, which keeps the L2-to-SM traffic (the practical limit of this kernel) at
+// 131 flop per byte.
 //
 // Roles inside one 192-thread CTA (one output tile per CTA):
-//   warp 0, one lane : TMA producer. cp.async.bulk.tensor.2d loads of the W tile (128 x 64) and the x tile (256 x 64),
-//                      both K-major with the 128-byte swizzle, into a 4-stage ring; completion by mbarrier tx bytes.
-//   warp 1, one lane : MMA issuer. Four tcgen05.mma (K = 16 each) per stage from shared-memory descriptors, then
-//                      tcgen05.commit on the stage's "empty" barrier; after the last stage a commit on "accumulator full".
+//   warp 0, one lane : TMA producer. cp.async.bulk.tensor.2d loads of the W tile (256 x 64, as two boxes of 128 rows) and
+//                      the x tile (256 x 64), K-major with the 128-byte swizzle, into a 3-stage ring; completion by
+//                      mbarrier tx bytes.
+//   warp 1, one lane : MMA issuer. Eight tcgen05.mma per stage (two row halves x four K = 16 slices) from shared-memory
+//                      descriptors, then tcgen05.commit on the stage's "empty" barrier; after the last stage a commit
+//                      on "accumulator full".
 //   warps 2..5       : epilogue. tcgen05.ld (32 lanes x 32 columns per instruction) of the warp's quarter of the 128
-//                      accumulator rows, coalesced fp32 stores of z (32 consecutive rows per token and warp).
-// Warp 1 also allocates and frees the 256 TMEM columns. No TMA multicast, no peer memory. Every mbarrier wait is bounded:
+//                      lanes of each accumulator, coalesced fp32 stores of z (32 consecutive rows per token and warp).
+// Warp 1 also allocates and frees the 512 TMEM columns. No TMA multicast, no peer memory. Every mbarrier wait is bounded:
 // on a time-out the CTA raises a flag in shared memory and in the caller's status word, all roles fall through, TMEM is
 // freed and the kernel returns (the result is then invalid and the host reports QTIP_E_KERNEL).
 #include <cuda.h>
@@ -17,9 +22,10 @@
 
 namespace qb {
 
-constexpr int kTcM = 128, kTcN = 256, kTcK = 64, kTcStages = 4;
+constexpr int kTcM = 128, kTcN = 256, kTcK = 64, kTcStages = 3;
+constexpr int kTcHalves = 2;  // 128-row accumulators per CTA (out must be a multiple of 128; a last odd half is skipped)
 constexpr int kTcThreads = 192;
-constexpr uint32_t kTcABytes = kTcM * kTcK * 2, kTcBBytes = kTcN * kTcK * 2;  // 16 KiB + 32 KiB per stage
+constexpr uint32_t kTcABytes = kTcHalves * kTcM * kTcK * 2, kTcBBytes = kTcN * kTcK * 2;  // 32 KiB + 32 KiB per stage
 constexpr long long kTcWaitCycles = 2000000000LL;
 
 struct TcSmem {
@@ -97,13 +103,14 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 float* __restrict__ z, int stride, int k_steps, int tokens,
-                                                                int* __restrict__ status) {
+                                                                int out, int* __restrict__ status) {
   extern __shared__ unsigned char tc_smem_raw[];
   const uint32_t raw = smem_u32(tc_smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;  // swizzled tiles need 1,024-byte alignment
   TcSmem& sm = *reinterpret_cast<TcSmem*>(tc_smem_raw + (tiles - raw) + size_t(kTcStages) * (kTcABytes + kTcBBytes));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * kTcM, tok0 = blockIdx.y * kTcN;
+  const int row0 = blockIdx.x * (kTcHalves * kTcM), tok0 = blockIdx.y * kTcN;
+  const int halves = min(kTcHalves, (out - row0) / kTcM);  // 1 for the last tile when out / 128 is odd
   volatile int* abort_flag = &sm.abort_flag;
 
   if (threadIdx.x == 0) {
@@ -115,9 +122,9 @@ __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_kernel(const __grid_con
     sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {  // TMEM allocation: whole warp, 256 columns (power of two >= 32)
+  if (warp == 1) {  // TMEM allocation: whole warp, all 512 columns (two 128 x 256 fp32 accumulators)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
-                 "r"(uint32_t(kTcN))
+                 "r"(uint32_t(kTcHalves * kTcN))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -132,9 +139,10 @@ __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_kernel(const __grid_con
       const int s = k % kTcStages;
       if (k >= kTcStages && !tc_wait(smem_u32(&sm.empty[s]), uint32_t((k / kTcStages - 1) & 1), abort_flag, status)) break;
       const uint32_t bar = smem_u32(&sm.full[s]);
-      tc_mbar_expect_tx(bar, kTcABytes + kTcBBytes);
+      tc_mbar_expect_tx(bar, uint32_t(halves) * (kTcABytes / kTcHalves) + kTcBBytes);
       const uint32_t a_dst = tiles + uint32_t(s) * (kTcABytes + kTcBBytes);
-      tc_tma_load_2d(a_dst, &map_w, k * kTcK, row0, bar);
+      for (int h = 0; h < halves; ++h)
+        tc_tma_load_2d(a_dst + uint32_t(h) * (kTcABytes / kTcHalves), &map_w, k * kTcK, row0 + h * kTcM, bar);
       tc_tma_load_2d(a_dst + kTcABytes, &map_x, k * kTcK, tok0, bar);
     }
   } else if (warp == 1 && lane == 0) {
@@ -146,10 +154,14 @@ __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_kernel(const __grid_con
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_addr = tiles + uint32_t(s) * (kTcABytes + kTcBBytes);
-      const uint64_t a_desc = tc_smem_desc(a_addr), b_desc = tc_smem_desc(a_addr + kTcABytes);
+      const uint64_t b_desc = tc_smem_desc(a_addr + kTcABytes);
+      for (int h = 0; h < halves; ++h) {
+        const uint64_t a_desc = tc_smem_desc(a_addr + uint32_t(h) * (kTcABytes / kTcHalves));
 #pragma unroll
-      for (int kk = 0; kk < kTcK / 16; ++kk)  // 16 bf16 = 32 bytes = 2 descriptor units along K inside the swizzled row
-        tc_mma(tmem, a_desc + uint64_t(2 * kk), b_desc + uint64_t(2 * kk), kTcIdesc, k > 0 || kk > 0);
+        for (int kk = 0; kk < kTcK / 16; ++kk)  // 16 bf16 = 32 bytes = 2 descriptor units along K inside the swizzled row
+          tc_mma(tmem + uint32_t(h * kTcN), a_desc + uint64_t(2 * kk), b_desc + uint64_t(2 * kk), kTcIdesc,
+                 k > 0 || kk > 0);
+      }
       tc_commit(smem_u32(&sm.empty[s]));  // frees the stage once these MMAs have read it
     }
     if (ok) tc_commit(smem_u32(&sm.acc_full));
@@ -159,11 +171,12 @@ __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_kernel(const __grid_con
     const bool ok = tc_wait(smem_u32(&sm.acc_full), 0, abort_flag, status);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
-      const int row = row0 + q * 32 + lane;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kTcN; c0 += 32) {
+      for (int cc = 0; cc < halves * kTcN; cc += 32) {
+        const int h = cc / kTcN, c0 = cc % kTcN;
+        const int row = row0 + h * kTcM + q * 32 + lane;
         uint32_t v[32];
-        const uint32_t taddr = tmem + (uint32_t(q * 32) << 16) + uint32_t(c0);
+        const uint32_t taddr = tmem + (uint32_t(q * 32) << 16) + uint32_t(cc);
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -187,7 +200,7 @@ __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_kernel(const __grid_con
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kTcN)) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kTcHalves * kTcN)) : "memory");
   }
 }
 
@@ -242,10 +255,10 @@ extern "C" int qtip_prefill_gemm(const uint16_t* w_dense_d, const uint16_t* x_d,
   if (rc) return rc;
   rc = make_map(&map_x, x_d, uint64_t(tokens), uint64_t(in), kTcN);
   if (rc) return rc;
-  const dim3 grid(out / kTcM, (tokens + kTcN - 1) / kTcN);
+  const dim3 grid((out / kTcM + kTcHalves - 1) / kTcHalves, (tokens + kTcN - 1) / kTcN);
   QB_REQUIRE(grid.y <= 65535, QTIP_E_GEOMETRY, "qtip_prefill_gemm: too many tokens (%d)", tokens);
   gemm_tc_kernel<<<grid, kTcThreads, kTcSmemBytes, as_stream(stream)>>>(map_w, map_x, z_d, stride, in / kTcK, tokens,
-                                                                        status_d);
+                                                                        out, status_d);
   QB_LAUNCHED();
   return QTIP_OK;
 }
