@@ -21,10 +21,13 @@ _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 
 
 def build(ref=False):
-    """Compile the oracle (and, with ref=True and the reference tree present, the reference's CPU code)."""
+    """Compile the oracle (and, with ref=True and the reference tree present, the reference's CPU code and, when nvcc is
+    there, the reference's CUDA kernels for this path)."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
     if ref and os.path.isdir("/root/reference/src"):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref"], stderr=subprocess.DEVNULL)
+        if os.path.exists("/usr/local/cuda/bin/nvcc"):
+            subprocess.check_call(["make", "-s", "-C", _HERE, "refgpu"], stderr=subprocess.DEVNULL)
 
 
 def _load(path):
@@ -377,3 +380,84 @@ class Reference:
                                  int(device_rounding), int(round_z), y):
             raise ValueError("reference_forward failed")
         return y
+
+
+class ReferenceGpu:
+    """The reference's own CUDA kernels for this path, compiled in place for sm_100a (Makefile target `refgpu`).
+
+    Every pointer argument is a raw device address (an int, e.g. a torch tensor's data_ptr()); `stream` is a
+    cudaStream_t as an int (0 = the default stream). Encode-side errors abort the process, as in the reference; the
+    runtime-side wrappers raise RuntimeError with the reference's message. `available` is False when the prebuilt
+    files are absent."""
+
+    def __init__(self):
+        self.enc = _load(os.path.join(_HERE, "_ref", "libqtip_ref_gpu_encode.so"))
+        self.dec = _load(os.path.join(_HERE, "_ref", "libqtip_ref_gpu_decode.so"))
+        self.available = self.enc is not None and self.dec is not None
+        P, I, L = C.c_void_p, C.c_int, C.c_long
+        if self.enc is not None:
+            E = self.enc
+            E.refgpu_ldlq_prep.argtypes = [P, P, P, P, L, L, I, I, P, P]
+            E.refgpu_viterbi_fwd.argtypes = [P, P, I, I, P, P, P, P]
+            E.refgpu_viterbi_overlap.argtypes = [P, P, I, P, P]
+            E.refgpu_viterbi_finish.argtypes = [P, P, I, I, P, I, I, P, L, I, P, P]
+            E.refgpu_decode_states.argtypes = [P, I, P, P, P]
+            for f in (E.refgpu_ldlq_prep, E.refgpu_viterbi_fwd, E.refgpu_viterbi_overlap, E.refgpu_viterbi_finish,
+                      E.refgpu_decode_states):
+                f.restype = None
+        if self.dec is not None:
+            D = self.dec
+            D.refgpu_last_error.restype = C.c_char_p
+            M = [P, P, P, P, I, I]  # trellis, su, sv, lut, in, out
+            D.refgpu_qtip_prepare.argtypes = M + [P, P, P, P, I, I]
+            D.refgpu_qtip_multiply.argtypes = M + [P, P, I, I, P, I]
+            D.refgpu_qtip_finish.argtypes = M + [P, P, P, I, I, P, I, I]
+            D.refgpu_qtip_forward.argtypes = M + [P, P, P, P, P, I, P, I]
+            D.refgpu_qtip_multiply_batch.argtypes = M + [P, P, I, I, I, P, I]
+            D.refgpu_qtip_decode_matrix.argtypes = M + [P, P]
+            D.refgpu_fp8_forward.argtypes = [P, P, P, P, I, I, P]
+
+    def _rt(self, rc):
+        if rc:
+            raise RuntimeError(self.dec.refgpu_last_error().decode())
+
+    # ---- encode side (src/gpu.hpp:276-292)
+    def ldlq_prep(self, WT, hatWT, prod, L, n, m, col0, bufend, X, stream=0):
+        self.enc.refgpu_ldlq_prep(WT, hatWT, prod, L, n, m, col0, bufend, X, stream)
+
+    def viterbi_fwd(self, X, overlap, roll, B, A, final_state, lut_h2, stream=0):
+        self.enc.refgpu_viterbi_fwd(X, overlap, roll, B, A, final_state, lut_h2, stream)
+
+    def viterbi_overlap(self, A, final_state, B, overlap, stream=0):
+        self.enc.refgpu_viterbi_overlap(A, final_state, B, overlap, stream)
+
+    def viterbi_finish(self, A, final_state, B, b0, Q, nblk, blk, hatWT, m, col0, lut_h2, stream=0):
+        self.enc.refgpu_viterbi_finish(A, final_state, B, b0, Q, nblk, blk, hatWT, m, col0, lut_h2, stream)
+
+    def decode_states(self, states, B, hat, lut_h2, stream=0):
+        self.enc.refgpu_decode_states(states, B, hat, lut_h2, stream)
+
+    # ---- runtime side (runtime/cuda/kernels.hpp:5-24, runtime/cuda/batch_kernels.hpp:5-8); w = (trellis, su, sv, lut, in, out)
+    def initialize_tables(self):
+        self._rt(self.dec.refgpu_initialize_tables())
+
+    def qtip_prepare(self, w, x, scratch, rotated, tokens=1, rank_major=False, stream=0):
+        self._rt(self.dec.refgpu_qtip_prepare(*w, x, scratch, rotated, stream, tokens, int(rank_major)))
+
+    def qtip_multiply(self, w, rotated, z, stride, splits, tokens=1, stream=0):
+        self._rt(self.dec.refgpu_qtip_multiply(*w, rotated, z, stride, splits, stream, tokens))
+
+    def qtip_finish(self, w, z, y, scratch, round_z, splits, tokens=1, rank_major=False, stream=0):
+        self._rt(self.dec.refgpu_qtip_finish(*w, z, y, scratch, int(round_z), splits, stream, tokens, int(rank_major)))
+
+    def qtip_forward(self, w, x, y, scratch, rotated, z, round_z, splits=1, stream=0):
+        self._rt(self.dec.refgpu_qtip_forward(*w, x, y, scratch, rotated, z, int(round_z), stream, splits))
+
+    def qtip_multiply_batch(self, w, rotated, z, stride, splits, tokens, implementation=-1, stream=0):
+        self._rt(self.dec.refgpu_qtip_multiply_batch(*w, rotated, z, stride, splits, tokens, stream, implementation))
+
+    def qtip_decode_matrix(self, w, dense, stream=0):
+        self._rt(self.dec.refgpu_qtip_decode_matrix(*w, dense, stream))
+
+    def fp8_forward(self, wq, scale, x, y, n_in, n_out, stream=0):
+        self._rt(self.dec.refgpu_fp8_forward(wq, scale, x, y, n_in, n_out, stream))
