@@ -121,6 +121,75 @@ def cpu_reference_rate(seconds_target, X, tlut_bits):
             "sample": "%d of the %d tiles of the workload, %.1f s" % (n, len(X), dt)}
 
 
+def reference_gpu_rates(pkg, torch):
+    """The reference's own CUDA kernels (compiled in place for sm_100a, test infrastructure under oracle/_ref) timed on
+    this GPU beside ours, as a second reported baseline: its two-pass Viterbi on 4,096 tiles (the size of its own
+    --bench run) and its batch-1 operator on the 57344 x 12288 matrix. CUDA events, launches queued back to back."""
+    from oracle.oracle import ReferenceGpu
+    R = ReferenceGpu()
+    if not R.available:
+        return {"unavailable": "oracle/_ref holds no build of the reference's CUDA kernels"}
+    synth, codec, linear = pkg.synth, pkg.codec, pkg.linear
+    p = lambda t: None if t is None else t.data_ptr()  # noqa: E731
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    tiles, batch = 4096, 1024
+    X = torch.from_numpy(synth.tile_sequences(synth.gaussian_matrix(256, tiles, 2))).cuda()  # 16 x (tiles / 16) tiles
+    lut_d, _ = codec.device_lut(synth.seeded_tlut(1))
+    A = torch.empty((batch, 127, 1024), dtype=torch.int16, device="cuda")
+    fs = torch.empty(batch, dtype=torch.int16, device="cuda")
+    ov = torch.empty(batch, dtype=torch.int32, device="cuda")
+    Q = torch.empty((tiles, 128), dtype=torch.int16, device="cuda")
+    hat = torch.empty((16, 16 * tiles), dtype=torch.float32, device="cuda")
+
+    def ref_quantize():
+        for b0 in range(0, tiles, batch):
+            x = X[b0:b0 + batch]
+            R.viterbi_fwd(p(x), None, 1, batch, p(A), p(fs), p(lut_d))
+            R.viterbi_overlap(p(A), p(fs), batch, p(ov))
+            R.viterbi_fwd(p(x), p(ov), 0, batch, p(A), p(fs), p(lut_d))
+            R.viterbi_finish(p(A), p(fs), batch, b0, p(Q), 1, 0, p(hat), 16 * tiles, 0, p(lut_d))
+
+    vit_ms = timed(ref_quantize, 2)
+    ours_states, _ = codec.quantize_tiles(X, lut_d)
+    same = bool(torch.equal(ours_states, Q))
+    del A, hat
+    res = {"viterbi_weights_per_s": tiles * 256 / (vit_ms * 1e-3), "viterbi_sample": "%d tiles, batches of %d" % (tiles, batch),
+           "viterbi_codes_identical_to_ours": same}
+
+    n_in, n_out = 12288, 57344
+    R.initialize_tables()
+    trellis = torch.from_numpy(synth.random_trellis(n_out, n_in, 4).view(np.int16)).cuda()
+    su, sv = (torch.from_numpy(synth.signs(n, 5 + i)).cuda() for i, n in enumerate((n_in, n_out)))
+    w = linear.Matrix(trellis, su, sv, linear.runtime_lut(synth.seeded_tlut(1)), n_in, n_out)
+    wr = (p(w.trellis), p(w.su), p(w.sv), p(w.lut), n_in, n_out)
+    x = torch.randn(n_in, device="cuda").to(torch.bfloat16)
+    rot = torch.empty(n_in, dtype=torch.bfloat16, device="cuda")
+    y = torch.empty(n_out, dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty(n_out, dtype=torch.float32, device="cuda")
+    z = torch.empty((32, n_out), dtype=torch.float32, device="cuda")
+    R.qtip_prepare(wr, p(x), p(scratch), p(rot))
+    best = None
+    for splits in (1, 2, 4, 8, 16, 32):
+        mus = timed(lambda: R.qtip_multiply(wr, p(rot), p(z), n_out, splits), 20) * 1e3
+        fus = timed(lambda: R.qtip_forward(wr, p(x), p(y), p(scratch), p(rot), p(z), False, splits), 20) * 1e3
+        if best is None or fus < best["gemv_forward_us"]:
+            best = {"gemv_splits": splits, "gemv_multiply_us": mus, "gemv_forward_us": fus}
+    res.update(best)
+    res["kind"] = "the reference's CUDA kernels recompiled for sm_100a, same GPU, same inputs"
+    return res
+
+
 def reference_arm(args):
     """The reference's CPU implementation of the path on the host cores, same config and metric."""
     rank = int(os.environ.get("RANK", "0"))
@@ -325,6 +394,10 @@ def main():
     if not args.no_extras and world == 1:
         Xs = synth.tile_sequences(synth.gaussian_matrix(256, 4096 * 16, 2))
         line["cpu_baseline"] = cpu_reference_rate(12.0, Xs, tl.view(np.uint16))
+        try:
+            line["reference_gpu"] = reference_gpu_rates(pkg, torch)
+        except Exception as ex:
+            line["reference_gpu"] = {"error": repr(ex)}
     print(json.dumps(line))
     if world > 1:
         dist.barrier()
