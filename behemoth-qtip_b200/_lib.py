@@ -22,7 +22,13 @@ class QtipMatrix(C.Structure):
                 ("n_in", C.c_int), ("n_out", C.c_int)]
 
 
+class QtipTpExchange(C.Structure):
+    """POD mirror of qtip_tp_exchange: every rank's exchange buffer as addressable from this process."""
+    _fields_ = [("base", C.c_void_p * 8), ("bytes", C.c_size_t), ("rank", C.c_int), ("ranks", C.c_int)]
+
+
 _P, _I, _L, _Z, _F = C.c_void_p, C.c_int, C.c_long, C.c_size_t, C.c_float
+_X = C.POINTER(QtipTpExchange)
 
 # name -> argument types; every function returns int except where noted in _RESTYPES
 SIGNATURES = {
@@ -70,12 +76,22 @@ SIGNATURES = {
     "qtip_fp8_forward": [_P, _P, _P, _P, _I, _I, _I, _P],
     "qtip_reduce_products": [_P, _Z, _I, _P],
     "qtip_reduce_to_b16": [_P, _P, _P, _Z, _I, _I, _P],
+    "qtip_tp_alloc": [_Z, C.POINTER(C.c_void_p)],
+    "qtip_tp_free": [_P],
+    "qtip_tp_export": [_P, C.c_char_p],
+    "qtip_tp_import": [C.c_char_p, C.POINTER(C.c_void_p)],
+    "qtip_tp_close": [_P],
+    "qtip_tp_reset": [_X, _P],
+    "qtip_multiply_push": [QtipMatrix, _P, _X, _I, _I, _I, _I, _P, _I],
+    "qtip_gather_wait": [_X, _I, C.POINTER(C.c_void_p), _P],
+    "qtip_tp_status": [_X, _P],
 }
 _RESTYPES = {
     "qtip_last_error": (C.c_char_p, []),
     "qtip_abi_version": (C.c_int, []),
     "qtip_quantize_workspace_bytes": (C.c_size_t, [_I]),
     "qtip_ldlq_workspace_bytes": (C.c_size_t, [_L, _L]),
+    "qtip_tp_exchange_bytes": (C.c_size_t, [_I, _I, _I]),
 }
 
 

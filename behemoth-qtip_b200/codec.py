@@ -29,6 +29,8 @@ def init():
 def _p(t, dtype=None):
     if t is None:
         return None
+    if isinstance(t, int):  # a raw device address (a slot of a tensor-parallel exchange buffer)
+        return C.c_void_p(t)
     assert t.is_cuda and t.is_contiguous(), "device-resident contiguous tensor expected"
     if dtype is not None:
         assert t.dtype == dtype, "expected %s, got %s" % (dtype, t.dtype)

@@ -14,6 +14,8 @@
 // so results are deterministic; a CTA runs four items at a time and walks the item list persistently.
 #include <mma.h>
 
+#include <cstring>
+
 #include "common.cuh"
 
 namespace qb {
@@ -59,6 +61,23 @@ __device__ __forceinline__ void decode_window(uint32_t u, uint32_t lane, uint32_
   }
 }
 
+// Tensor-parallel push: the products of this rank's rows go straight into every rank's gathered buffer (plain stores
+// to peer memory) instead of a local z, and the last CTA of the launch raises this rank's flag on every rank.
+constexpr int kTpMaxRanks = QTIP_TP_MAX_RANKS;
+struct TpPush {
+  float* z[kTpMaxRanks];        // rank p's gathered buffer of the slot, already offset to this rank's first row
+  unsigned* flag[kTpMaxRanks];  // rank p's flag word of (slot, this rank)
+  unsigned* ctl;                // this rank's control block (TpControl)
+  int ranks, slot, signal;
+};
+// Control block at the start of every exchange buffer. flags are written by the peers, the rest is local.
+struct TpControl {
+  unsigned flags[2][kTpMaxRanks];  // [slot][source rank]: epoch of the last complete push
+  unsigned done[2];                // [slot]: epoch of the last completed wait
+  unsigned counter;                // CTAs of the running push launch that have finished storing
+  unsigned status;                 // non-zero: a bounded wait ran out
+};
+
 struct ItemCtx {
   const uint2* codes;     // kernel-layout words as 8-byte units (word c of the four tiles of a block)
   const uint32_t* xw;     // rotated input, bf16 pairs, first token of this launch
@@ -69,8 +88,9 @@ struct ItemCtx {
 
 // One work item = one 32-row block-row x one K-split, shared by `nw` warps (this is warp `wi` of them): each warp takes
 // a contiguous run of 32x32 blocks, then the partial sums are added in warp order through `red` and written to z.
-template <int NT, bool XS>
-__device__ __forceinline__ void run_item(const ItemCtx& c, int item, int nw, int wi, int bar_id, float* red) {
+template <int NT, bool XS, bool PUSH>
+__device__ __forceinline__ void run_item(const ItemCtx& c, const TpPush& push, int item, int nw, int wi, int bar_id,
+                                         float* red) {
   constexpr int RT = XS ? 1 : NT * 8;  // tokens kept per warp in the reduction buffer
   const int lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
   const int br = item / c.splits, sp = item - br * c.splits;
@@ -176,7 +196,14 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, int item, int nw, int
     if (tok < c.tokens) {
       float s = red[o];
       for (int q = 1; q < nw; ++q) s += red[size_t(q) * RT * 32 + o];
-      c.z[(size_t(sp) * c.tokens_total + c.t0 + tok) * c.stride + br * 32 + row] = s;
+      const size_t at = (size_t(sp) * c.tokens_total + c.t0 + tok) * c.stride + br * 32 + row;
+      if constexpr (PUSH) {
+#pragma unroll
+        for (int p = 0; p < kTpMaxRanks; ++p)
+          if (p < push.ranks) push.z[p][at] = s;
+      } else {
+        c.z[at] = s;
+      }
     }
   }
   warps_sync(bar_id, nw);
@@ -187,10 +214,11 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, int item, int nw, int
 // token): the activations are staged in shared memory in fragment order, one 16-byte read per block and lane.
 // Work items are dealt round-robin to groups of 8 warps (4 per CTA) for as many full rounds as there are; the remainder
 // is done by whole CTAs (32 warps per item) so that the tail of the launch is a quarter of a round long.
-template <int NT, bool XS>
+template <int NT, bool XS, bool PUSH>
 __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matrix w, const uint16_t* __restrict__ x,
                                                                        float* __restrict__ z, int stride, int splits,
-                                                                       int tokens_total, int t0, int tokens) {
+                                                                       int tokens_total, int t0, int tokens,
+                                                                       const __grid_constant__ TpPush push) {
   unsigned char* smem = reinterpret_cast<unsigned char*>(gemm_smem_words);
   constexpr int RT = XS ? 1 : NT * 8;
   uint32_t* lut_s = gemm_smem_words;
@@ -218,10 +246,57 @@ __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matr
   const int n_grouped = n_items / slots * slots;
   const int grp = warp / kWarpsPerItem, wi = warp % kWarpsPerItem;
   for (int item = blockIdx.x * kItemsPerCta + grp; item < n_grouped; item += slots)
-    run_item<NT, XS>(c, item, kWarpsPerItem, wi, grp + 1, red + size_t(grp) * kWarpsPerItem * RT * 32);
+    run_item<NT, XS, PUSH>(c, push, item, kWarpsPerItem, wi, grp + 1, red + size_t(grp) * kWarpsPerItem * RT * 32);
   __syncthreads();
   for (int item = n_grouped + blockIdx.x; item < n_items; item += gridDim.x)
-    run_item<NT, XS>(c, item, kGemmThreads / 32, warp, 0, red);
+    run_item<NT, XS, PUSH>(c, push, item, kGemmThreads / 32, warp, 0, red);
+  if constexpr (PUSH) {
+    // Every thread orders its peer stores before the CTA's arrival on the local counter; the CTA that arrives last
+    // orders all arrivals before the flags it then raises on every rank. (Fences at system scope are cumulative.)
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+      TpControl* ctl = reinterpret_cast<TpControl*>(push.ctl);
+      if (atomicAdd(&ctl->counter, 1u) == gridDim.x - 1) {
+        *reinterpret_cast<volatile unsigned*>(&ctl->counter) = 0;
+        if (push.signal) {
+          const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&ctl->done[push.slot]) + 1u;
+          __threadfence_system();
+#pragma unroll
+          for (int p = 0; p < kTpMaxRanks; ++p)
+            if (p < push.ranks) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(push.flag[p]), "r"(epoch) : "memory");
+        }
+      }
+    }
+  }
+}
+
+// One warp: lane r waits (bounded) until rank r's push of the slot's next epoch has landed in this rank's buffer, then
+// lane 0 records the epoch as done. A wait that runs out leaves the epoch untouched and raises the status word.
+__global__ void tp_wait_kernel(unsigned* ctl_words, int slot, int ranks) {
+  TpControl* ctl = reinterpret_cast<TpControl*>(ctl_words);
+  const int lane = threadIdx.x;
+  const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&ctl->done[slot]) + 1u;
+  bool ok = true;
+  if (lane < ranks) {
+    const unsigned* f = &ctl->flags[slot][lane];
+    const long long start = clock64();
+    for (;;) {
+      unsigned v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if (v == epoch) break;
+      if (clock64() - start > 2000000000LL) {
+        ok = false;
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (lane == 0) {
+    if (ok) *reinterpret_cast<volatile unsigned*>(&ctl->done[slot]) = epoch;
+    else atomicExch(&ctl->status, 3u);
+  }
 }
 
 // Dense decode to bf16, row-major [out][in]: a CTA decodes a 32-row x 256-column strip through shared memory so that
@@ -283,10 +358,17 @@ static size_t gemm_smem(int nt, bool xs, int n_in) {
 }
 
 int decode_device_setup(DeviceInfo*) {
-  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMaxSmem)));
-  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               int(kMaxSmem)));
+  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                int(gemm_smem(1, false, 0))));
-  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<2, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               int(gemm_smem(2, false, 0))));
+  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               int(kMaxSmem)));
+  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               int(gemm_smem(1, false, 0))));
+  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                int(gemm_smem(2, false, 0))));
   return QTIP_OK;
 }
@@ -300,7 +382,9 @@ static int check_matrix(const qtip_matrix& w, const char* who, bool need_codes =
   return QTIP_OK;
 }
 
-static int multiply_impl(qtip_matrix w, const uint16_t* x, float* z, int stride, int splits, int tokens, cudaStream_t s) {
+template <bool PUSH>
+static int multiply_impl(qtip_matrix w, const uint16_t* x, float* z, int stride, int splits, int tokens, cudaStream_t s,
+                         TpPush push = TpPush{}) {
   const DeviceInfo* info = device_info();
   if (!info) return QTIP_E_DEVICE;
   const int n_items = (w.out / 32) * splits;
@@ -309,15 +393,16 @@ static int multiply_impl(qtip_matrix w, const uint16_t* x, float* z, int stride,
   const int per = tokens <= 8 ? 8 : 16;
   for (int t0 = 0; t0 < tokens; t0 += per) {
     const int nt = min(per, tokens - t0);
+    push.signal = t0 + per >= tokens;  // the flags go up after the last launch of the token walk
     if (tokens == 1 && gemm_smem(1, true, w.in) <= kMaxSmem)
-      trellis_gemm_kernel<1, true><<<ctas, kGemmThreads, gemm_smem(1, true, w.in), s>>>(w, x, z, stride, splits, tokens,
-                                                                                      t0, nt);
+      trellis_gemm_kernel<1, true, PUSH><<<ctas, kGemmThreads, gemm_smem(1, true, w.in), s>>>(w, x, z, stride, splits,
+                                                                                            tokens, t0, nt, push);
     else if (per == 8)
-      trellis_gemm_kernel<1, false><<<ctas, kGemmThreads, gemm_smem(1, false, 0), s>>>(w, x, z, stride, splits, tokens,
-                                                                                      t0, nt);
+      trellis_gemm_kernel<1, false, PUSH><<<ctas, kGemmThreads, gemm_smem(1, false, 0), s>>>(w, x, z, stride, splits,
+                                                                                            tokens, t0, nt, push);
     else
-      trellis_gemm_kernel<2, false><<<ctas, kGemmThreads, gemm_smem(2, false, 0), s>>>(w, x, z, stride, splits, tokens,
-                                                                                      t0, nt);
+      trellis_gemm_kernel<2, false, PUSH><<<ctas, kGemmThreads, gemm_smem(2, false, 0), s>>>(w, x, z, stride, splits,
+                                                                                            tokens, t0, nt, push);
     QB_LAUNCHED();
   }
   return QTIP_OK;
@@ -344,7 +429,7 @@ extern "C" int qtip_multiply(qtip_matrix w, const uint16_t* rotated_d, float* z_
   QB_REQUIRE(rotated_d && z_d && tokens >= 1, QTIP_E_ARG, "qtip_multiply: bad argument");
   QB_REQUIRE(stride >= w.out && splits >= 1 && splits <= 32 && splits <= w.in / 32, QTIP_E_GEOMETRY,
              "qtip_multiply: stride = %d, splits = %d invalid for %d x %d", stride, splits, w.out, w.in);
-  return multiply_impl(w, rotated_d, z_d, stride, splits, tokens, as_stream(stream));
+  return multiply_impl<false>(w, rotated_d, z_d, stride, splits, tokens, as_stream(stream));
 }
 extern "C" int qtip_finish(qtip_matrix w, const float* z_d, uint16_t* y_d, float* scratch_d, int round_z, int splits,
                            void* stream, int tokens, int rank_major) {
@@ -384,7 +469,7 @@ extern "C" int qtip_multiply_batch(qtip_matrix w, const uint16_t* x_d, float* z_
   QB_REQUIRE(x_d && z_d && tokens >= 1, QTIP_E_ARG, "qtip_multiply_batch: bad argument");
   QB_REQUIRE(stride >= w.out && splits >= 1 && splits <= 32 && splits <= w.in / 32, QTIP_E_GEOMETRY,
              "qtip_multiply_batch: stride = %d, splits = %d invalid for %d x %d", stride, splits, w.out, w.in);
-  return multiply_impl(w, x_d, z_d, stride, splits, tokens, as_stream(stream));
+  return multiply_impl<false>(w, x_d, z_d, stride, splits, tokens, as_stream(stream));
 }
 extern "C" int qtip_decode_matrix(qtip_matrix w, uint16_t* out_d, void* stream) {
   int rc = check_matrix(w, "qtip_decode_matrix");
@@ -410,5 +495,106 @@ extern "C" int qtip_reduce_to_b16(const float* x_d, const float* scale_d, uint16
   reduce_b16_kernel<<<blocks_for(long(elements), 256), 256, 0, as_stream(stream)>>>(x_d, scale_d, y_d, elements, width,
                                                                                     splits);
   QB_LAUNCHED();
+  return QTIP_OK;
+}
+
+// ---------------------------------------------------------------- tensor-parallel exchange (rotated-row sharding)
+// Exchange buffer of one rank: [TpControl, 256 bytes][gathered z, slot 0][gathered z, slot 1]; a slot holds
+// [split][token][out_full] fp32. Consecutive uses of an exchange alternate the two slots, so a rank that is already
+// pushing the next product never overwrites a buffer a slower rank is still transforming: rank r's push k + 2 follows
+// its wait k + 1, which saw rank p's push k + 1, which p's stream ordered after its output transform of step k.
+static_assert(sizeof(TpControl) <= 256, "control block");
+static size_t tp_slot_bytes(size_t exchange_bytes) { return (exchange_bytes - 256) / 2 / 256 * 256; }
+
+extern "C" size_t qtip_tp_exchange_bytes(int out_full, int max_tokens, int max_splits) {
+  if (out_full <= 0 || max_tokens <= 0 || max_splits <= 0) return 0;
+  const size_t slot = (size_t(out_full) * max_tokens * max_splits * 4 + 255) / 256 * 256;
+  return 256 + 2 * slot;
+}
+extern "C" int qtip_tp_alloc(size_t bytes, void** buf_d) {
+  QB_REQUIRE(buf_d && bytes >= 256 + 512, QTIP_E_ARG, "qtip_tp_alloc: bad argument");
+  QB_CUDA(cudaMalloc(buf_d, bytes));
+  QB_CUDA(cudaMemset(*buf_d, 0, bytes));
+  return QTIP_OK;
+}
+extern "C" int qtip_tp_free(void* buf_d) {
+  if (buf_d) QB_CUDA(cudaFree(buf_d));
+  return QTIP_OK;
+}
+extern "C" int qtip_tp_export(void* buf_d, unsigned char handle[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  QB_REQUIRE(buf_d && handle, QTIP_E_ARG, "qtip_tp_export: null pointer");
+  cudaIpcMemHandle_t h;
+  QB_CUDA(cudaIpcGetMemHandle(&h, buf_d));
+  std::memcpy(handle, &h, 64);
+  return QTIP_OK;
+}
+extern "C" int qtip_tp_import(const unsigned char handle[64], void** peer_d) {
+  QB_REQUIRE(handle && peer_d, QTIP_E_ARG, "qtip_tp_import: null pointer");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  QB_CUDA(cudaIpcOpenMemHandle(peer_d, h, cudaIpcMemLazyEnablePeerAccess));
+  return QTIP_OK;
+}
+extern "C" int qtip_tp_close(void* peer_d) {
+  if (peer_d) QB_CUDA(cudaIpcCloseMemHandle(peer_d));
+  return QTIP_OK;
+}
+static int check_exchange(const qtip_tp_exchange* ex, int slot, const char* who) {
+  QB_REQUIRE(ex && ex->ranks >= 1 && ex->ranks <= kTpMaxRanks && ex->rank >= 0 && ex->rank < ex->ranks, QTIP_E_ARG,
+             "%s: bad exchange (ranks 1..%d)", who, kTpMaxRanks);
+  QB_REQUIRE(slot == 0 || slot == 1, QTIP_E_ARG, "%s: slot must be 0 or 1", who);
+  QB_REQUIRE(ex->bytes >= 256 + 512, QTIP_E_WORKSPACE, "%s: exchange buffer too small", who);
+  for (int p = 0; p < ex->ranks; ++p)
+    QB_REQUIRE(ex->base[p] && reinterpret_cast<uintptr_t>(ex->base[p]) % 256 == 0, QTIP_E_ARG,
+               "%s: exchange base %d is null or not 256-byte aligned", who, p);
+  return QTIP_OK;
+}
+extern "C" int qtip_tp_reset(const qtip_tp_exchange* ex, void* stream) {
+  int rc = check_exchange(ex, 0, "qtip_tp_reset");
+  if (rc) return rc;
+  QB_CUDA(cudaMemsetAsync(ex->base[ex->rank], 0, 256, as_stream(stream)));
+  return QTIP_OK;
+}
+extern "C" int qtip_multiply_push(qtip_matrix w_shard, const uint16_t* rotated_d, const qtip_tp_exchange* ex, int slot,
+                                  int out_full, int row0, int splits, void* stream, int tokens) {
+  int rc = check_matrix(w_shard, "qtip_multiply_push");
+  if (rc) return rc;
+  if ((rc = check_exchange(ex, slot, "qtip_multiply_push"))) return rc;
+  QB_REQUIRE(rotated_d && tokens >= 1, QTIP_E_ARG, "qtip_multiply_push: bad argument");
+  QB_REQUIRE(splits >= 1 && splits <= 32 && splits <= w_shard.in / 32 && row0 >= 0 && row0 % 32 == 0 &&
+                 row0 + w_shard.out <= out_full,
+             QTIP_E_GEOMETRY, "qtip_multiply_push: rows [%d, %d) of %d, splits = %d", row0, row0 + w_shard.out, out_full,
+             splits);
+  const size_t slot_bytes = tp_slot_bytes(ex->bytes);
+  QB_REQUIRE(size_t(out_full) * tokens * splits * 4 <= slot_bytes, QTIP_E_WORKSPACE,
+             "qtip_multiply_push: %d x %d tokens x %d splits does not fit a slot of %zu bytes", out_full, tokens, splits,
+             slot_bytes);
+  TpPush push{};
+  for (int p = 0; p < ex->ranks; ++p) {
+    unsigned char* b = static_cast<unsigned char*>(ex->base[p]);
+    push.z[p] = reinterpret_cast<float*>(b + 256 + size_t(slot) * slot_bytes) + row0;
+    push.flag[p] = &reinterpret_cast<TpControl*>(b)->flags[slot][ex->rank];
+  }
+  push.ctl = static_cast<unsigned*>(ex->base[ex->rank]);
+  push.ranks = ex->ranks, push.slot = slot;
+  return multiply_impl<true>(w_shard, rotated_d, nullptr, out_full, splits, tokens, as_stream(stream), push);
+}
+extern "C" int qtip_gather_wait(const qtip_tp_exchange* ex, int slot, const float** z_gathered_d, void* stream) {
+  int rc = check_exchange(ex, slot, "qtip_gather_wait");
+  if (rc) return rc;
+  unsigned char* b = static_cast<unsigned char*>(ex->base[ex->rank]);
+  tp_wait_kernel<<<1, 32, 0, as_stream(stream)>>>(reinterpret_cast<unsigned*>(b), slot, ex->ranks);
+  QB_LAUNCHED();
+  if (z_gathered_d) *z_gathered_d = reinterpret_cast<const float*>(b + 256 + size_t(slot) * tp_slot_bytes(ex->bytes));
+  return QTIP_OK;
+}
+extern "C" int qtip_tp_status(const qtip_tp_exchange* ex, void* stream) {
+  int rc = check_exchange(ex, 0, "qtip_tp_status");
+  if (rc) return rc;
+  TpControl h;
+  QB_CUDA(cudaMemcpyAsync(&h, ex->base[ex->rank], sizeof h, cudaMemcpyDeviceToHost, as_stream(stream)));
+  QB_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  QB_REQUIRE(h.status == 0, QTIP_E_KERNEL, "tensor-parallel exchange: a wait for a peer's push ran out (status %u)", h.status);
   return QTIP_OK;
 }

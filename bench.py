@@ -678,14 +678,37 @@ def gemv_section(pkg, peaks, peak_src, rank, world):
         dist.all_gather_into_tensor(z_full, z_local)
         linear.qtip_finish(full, z_full, y, scratch, False, 1)
 
+    # The same projection with the gather fused into the product kernel: every rank's kernel stores its products into
+    # every rank's gathered buffer over NVLink (plain peer stores), a one-warp kernel waits for the peers' flags.
+    ex = pkg.tp.Exchange.from_process_group(n_out)
+    y_nccl = torch.empty_like(y)
+
+    def forward_fused():
+        pkg.tp.forward_tp(ex, full, shard, row0, x, y, scratch, rot)
+
+    forward_tp()
+    y_nccl.copy_(y)
+    forward_fused()
+    ex.check()
+    same = bool(torch.equal(y.view(torch.int16), y_nccl.view(torch.int16)))
     dist.barrier()
     fus = _time_us(forward_tp, 50, torch)
+    dist.barrier()
+    pus = _time_us(forward_fused, 50, torch)
+    ex.check()
+    dist.barrier()
     mus = _time_us(lambda: linear.qtip_multiply(shard, rot, z_local, rows, 1), 50, torch)
-    t = torch.tensor([fus, mus], device="cuda", dtype=torch.float64)
+    t = torch.tensor([fus, mus, pus, 0.0 if same else 1.0], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    fus, mus = float(t[0]), float(t[1])
-    res.update({"forward_us": fus, "multiply_us": mus, "forward_gbs": algo_bytes / fus / 1e3,
-                "multiply_gbs": algo_bytes / mus / 1e3, "collective": "ncclAllGather of z (fp32, %d B per rank)" % (rows * 4)})
+    fus, mus, pus, differ = float(t[0]), float(t[1]), float(t[2]), float(t[3])
+    dist.barrier()
+    ex.close()
+    res.update({"forward_us": pus, "forward_nccl_us": fus, "multiply_us": mus, "forward_gbs": algo_bytes / pus / 1e3,
+                "forward_nccl_gbs": algo_bytes / fus / 1e3, "multiply_gbs": algo_bytes / mus / 1e3,
+                "collective": "all-gather of z fused into the product kernel: peer stores over NVLink (fp32, %d B per "
+                              "rank and destination) + flag wait; forward_nccl_us is the same projection with "
+                              "ncclAllGather" % (rows * 4),
+                "fused_equals_nccl_bitwise": differ == 0.0})
     return res
 
 

@@ -215,6 +215,49 @@ int qtip_fp8_forward(const uint8_t* w_d, const float* scale_d, const uint16_t* x
  * the per-row scale). runtime/cuda/batch_kernels.cu:694-698,845-848 (decode_fp8_matrix). */
 int qtip_decode_fp8_matrix(const uint8_t* w_d, uint16_t* out_d, size_t elements, void* stream);
 
+/* ---- Tensor-parallel decode: rotated-row sharding with the gather fused into the product kernel --------------------
+ * Replaces, for the <= 16-token path, Rank::multiply + the ncclAllGather of z of runtime/cuda/tensor_model.cpp:444-502
+ * (sharding rule :105-124) and the peer_store copy of runtime/cuda/kernels.cu:402-411. Rank r holds the trellis words of
+ * output rows [r out/R, (r+1) out/R) (whole 32-row block-rows, see qtip_matrix) and the full SU / SV / LUT.
+ *
+ * Every rank owns one exchange buffer of qtip_tp_exchange_bytes() bytes that all ranks can address: base[p] is rank p's
+ * buffer as mapped in the calling process (peer access inside one process, or qtip_tp_export / qtip_tp_import between
+ * processes). It holds a 256-byte control block and two gathered-product slots, [split][token][out_full] fp32 each.
+ *
+ * qtip_multiply_push computes this rank's products and stores every finished 32-row piece directly into the slot of ALL
+ * ranks (plain peer stores, no staging copy, no collective call); the last CTA then raises this rank's flag on every
+ * rank. qtip_gather_wait enqueues a one-warp kernel that waits, for at most about a second, until every rank's flag
+ * shows the slot's next epoch, and returns the address of the local slot: the gathered z for qtip_finish (full matrix
+ * geometry, splits as pushed). Epochs live on the device, so the calls can be captured in a CUDA graph and replayed.
+ * Rule: consecutive uses of one exchange alternate slot 0 and 1 (also across graph replays), and every rank makes the
+ * same sequence of calls. A wait that runs out raises the status word (qtip_tp_status) and leaves the context usable.
+ * These entry points allocate nothing and do not synchronise the host; qtip_tp_alloc / qtip_tp_free / qtip_tp_export /
+ * qtip_tp_import / qtip_tp_close are set-up calls. */
+#define QTIP_TP_MAX_RANKS 8
+typedef struct qtip_tp_exchange {
+  void* base[QTIP_TP_MAX_RANKS]; /* every rank's exchange buffer (device addresses valid in this process) */
+  size_t bytes;                  /* size of each buffer */
+  int rank, ranks;
+} qtip_tp_exchange;
+size_t qtip_tp_exchange_bytes(int out_full, int max_tokens, int max_splits);
+/* cudaMalloc + zero fill of an exchange buffer (an allocation of its own, so that it can be exported). */
+int qtip_tp_alloc(size_t bytes, void** buf_d);
+int qtip_tp_free(void* buf_d);
+/* Inter-process handle (64 bytes) of a buffer from qtip_tp_alloc, and its mapping in another process of the same node. */
+int qtip_tp_export(void* buf_d, unsigned char handle[64]);
+int qtip_tp_import(const unsigned char handle[64], void** peer_d);
+int qtip_tp_close(void* peer_d);
+/* Zeroes the local control block (epochs, flags, status). All ranks call it, then synchronise with one another on the
+ * host, before the first push. */
+int qtip_tp_reset(const qtip_tp_exchange* ex, void* stream);
+/* Products of w_shard (rows [row0, row0 + w_shard.out) of a matrix of out_full rows) pushed to every rank. tokens <= the
+ * max_tokens the exchange was sized for; rotated_d as for qtip_multiply. */
+int qtip_multiply_push(qtip_matrix w_shard, const uint16_t* rotated_d, const qtip_tp_exchange* ex, int slot, int out_full,
+                       int row0, int splits, void* stream, int tokens);
+int qtip_gather_wait(const qtip_tp_exchange* ex, int slot, const float** z_gathered_d, void* stream);
+/* Synchronises `stream`; QTIP_E_KERNEL if a wait of this rank ran out since the last reset. */
+int qtip_tp_status(const qtip_tp_exchange* ex, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
