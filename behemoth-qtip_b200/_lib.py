@@ -82,7 +82,8 @@ SIGNATURES = {
     "qtip_tp_import": [C.c_char_p, C.POINTER(C.c_void_p)],
     "qtip_tp_close": [_P],
     "qtip_tp_reset": [_X, _P],
-    "qtip_multiply_push": [QtipMatrix, _P, _X, _I, _I, _I, _I, _P, _I],
+    "qtip_multiply_push": [QtipMatrix, _P, _X, _I, _I, _I, _I, _P, _I, _I],
+    "qtip_gathered_products": [_X, _I, C.POINTER(C.c_void_p)],
     "qtip_gather_wait": [_X, _I, C.POINTER(C.c_void_p), _P],
     "qtip_tp_status": [_X, _P],
 }

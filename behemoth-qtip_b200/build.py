@@ -42,7 +42,7 @@ def build(force=False, verbose=False):
         if p.returncode:
             raise RuntimeError("nvcc failed on %s" % src)
         objs.append(obj)
-    subprocess.check_call([NVCC, "-shared", "-o", LIB, *objs, "-ccbin", "/usr/bin/g++"])
+    subprocess.check_call([NVCC, "-shared", "-Wno-deprecated-gpu-targets", "-o", LIB, *objs, "-ccbin", "/usr/bin/g++"])
     return LIB
 
 

@@ -69,6 +69,7 @@ struct TpPush {
   unsigned* flag[kTpMaxRanks];  // rank p's flag word of (slot, this rank)
   unsigned* ctl;                // this rank's control block (TpControl)
   int ranks, slot, signal;
+  int wait;  // the last CTA also waits for the peers' flags (only when every rank runs on a GPU of its own)
 };
 // Control block at the start of every exchange buffer. flags are written by the peers, the rest is local.
 struct TpControl {
@@ -209,6 +210,31 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, const TpPush& push, i
   warps_sync(bar_id, nw);
 }
 
+// One warp: lane r waits (bounded) until rank r's push of the slot's next epoch has landed in this rank's buffer, then
+// lane 0 records the epoch as done. A wait that runs out leaves the epoch untouched and raises the status word.
+__device__ __forceinline__ void tp_wait_warp(TpControl* ctl, int slot, int ranks) {
+  const int lane = threadIdx.x & 31;
+  const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&ctl->done[slot]) + 1u;
+  bool ok = true;
+  if (lane < ranks) {
+    const unsigned* f = &ctl->flags[slot][lane];
+    const long long start = clock64();
+    for (;;) {
+      if (*reinterpret_cast<const volatile unsigned*>(f) == epoch) break;
+      if (clock64() - start > 2000000000LL) {
+        ok = false;
+        break;
+      }
+    }
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  __threadfence_system();  // the flags were read before, the gathered products are read after (by the next kernel)
+  if (lane == 0) {
+    if (ok) *reinterpret_cast<volatile unsigned*>(&ctl->done[slot]) = epoch;
+    else atomicExch(&ctl->status, 3u);
+  }
+}
+
 // z[(split * tokens_total + token) * stride + row]; x: [tokens_total][in] bf16 (the rotated input). One launch covers
 // tokens [t0, t0 + tokens), tokens <= 8 NT: each group of 8 tokens is one MMA column block held in registers. XS (one
 // token): the activations are staged in shared memory in fragment order, one 16-byte read per block and lane.
@@ -251,12 +277,16 @@ __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matr
   for (int item = n_grouped + blockIdx.x; item < n_items; item += gridDim.x)
     run_item<NT, XS, PUSH>(c, push, item, kGemmThreads / 32, warp, 0, red);
   if constexpr (PUSH) {
-    // Every thread orders its peer stores before the CTA's arrival on the local counter; the CTA that arrives last
-    // orders all arrivals before the flags it then raises on every rank. (Fences at system scope are cumulative.)
-    __threadfence_system();
+    // The barrier orders every thread's peer stores before thread 0's fence (fences are cumulative), the fence orders
+    // them before the CTA's arrival on the local counter; the CTA that arrives last fences once more (observing all
+    // arrivals, releasing all stores) and raises this rank's flag on every rank. With push.wait its first warp then
+    // waits for the peers' flags itself, which saves the separate wait kernel.
+    volatile uint32_t& wait_here = gemm_smem_words[0];  // the table is no longer needed once every warp is past the barrier
     __syncthreads();
     if (tid == 0) {
       TpControl* ctl = reinterpret_cast<TpControl*>(push.ctl);
+      bool last = false;
+      __threadfence_system();
       if (atomicAdd(&ctl->counter, 1u) == gridDim.x - 1) {
         *reinterpret_cast<volatile unsigned*>(&ctl->counter) = 0;
         if (push.signal) {
@@ -264,39 +294,19 @@ __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matr
           __threadfence_system();
 #pragma unroll
           for (int p = 0; p < kTpMaxRanks; ++p)
-            if (p < push.ranks) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(push.flag[p]), "r"(epoch) : "memory");
+            if (p < push.ranks) *reinterpret_cast<volatile unsigned*>(push.flag[p]) = epoch;
+          last = true;
         }
       }
+      wait_here = (last && push.wait) ? 1u : 0u;
     }
+    __syncthreads();
+    if (wait_here && warp == 0) tp_wait_warp(reinterpret_cast<TpControl*>(push.ctl), push.slot, push.ranks);
   }
 }
 
-// One warp: lane r waits (bounded) until rank r's push of the slot's next epoch has landed in this rank's buffer, then
-// lane 0 records the epoch as done. A wait that runs out leaves the epoch untouched and raises the status word.
 __global__ void tp_wait_kernel(unsigned* ctl_words, int slot, int ranks) {
-  TpControl* ctl = reinterpret_cast<TpControl*>(ctl_words);
-  const int lane = threadIdx.x;
-  const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&ctl->done[slot]) + 1u;
-  bool ok = true;
-  if (lane < ranks) {
-    const unsigned* f = &ctl->flags[slot][lane];
-    const long long start = clock64();
-    for (;;) {
-      unsigned v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-      if (v == epoch) break;
-      if (clock64() - start > 2000000000LL) {
-        ok = false;
-        break;
-      }
-      __nanosleep(100);
-    }
-  }
-  ok = __all_sync(0xffffffffu, ok);
-  if (lane == 0) {
-    if (ok) *reinterpret_cast<volatile unsigned*>(&ctl->done[slot]) = epoch;
-    else atomicExch(&ctl->status, 3u);
-  }
+  tp_wait_warp(reinterpret_cast<TpControl*>(ctl_words), slot, ranks);
 }
 
 // Dense decode to bf16, row-major [out][in]: a CTA decodes a 32-row x 256-column strip through shared memory so that
@@ -557,7 +567,7 @@ extern "C" int qtip_tp_reset(const qtip_tp_exchange* ex, void* stream) {
   return QTIP_OK;
 }
 extern "C" int qtip_multiply_push(qtip_matrix w_shard, const uint16_t* rotated_d, const qtip_tp_exchange* ex, int slot,
-                                  int out_full, int row0, int splits, void* stream, int tokens) {
+                                  int out_full, int row0, int splits, void* stream, int tokens, int wait) {
   int rc = check_matrix(w_shard, "qtip_multiply_push");
   if (rc) return rc;
   if ((rc = check_exchange(ex, slot, "qtip_multiply_push"))) return rc;
@@ -577,7 +587,7 @@ extern "C" int qtip_multiply_push(qtip_matrix w_shard, const uint16_t* rotated_d
     push.flag[p] = &reinterpret_cast<TpControl*>(b)->flags[slot][ex->rank];
   }
   push.ctl = static_cast<unsigned*>(ex->base[ex->rank]);
-  push.ranks = ex->ranks, push.slot = slot;
+  push.ranks = ex->ranks, push.slot = slot, push.wait = wait != 0;
   return multiply_impl<true>(w_shard, rotated_d, nullptr, out_full, splits, tokens, as_stream(stream), push);
 }
 extern "C" int qtip_gather_wait(const qtip_tp_exchange* ex, int slot, const float** z_gathered_d, void* stream) {
@@ -587,6 +597,14 @@ extern "C" int qtip_gather_wait(const qtip_tp_exchange* ex, int slot, const floa
   tp_wait_kernel<<<1, 32, 0, as_stream(stream)>>>(reinterpret_cast<unsigned*>(b), slot, ex->ranks);
   QB_LAUNCHED();
   if (z_gathered_d) *z_gathered_d = reinterpret_cast<const float*>(b + 256 + size_t(slot) * tp_slot_bytes(ex->bytes));
+  return QTIP_OK;
+}
+extern "C" int qtip_gathered_products(const qtip_tp_exchange* ex, int slot, const float** z_gathered_d) {
+  int rc = check_exchange(ex, slot, "qtip_gathered_products");
+  if (rc) return rc;
+  QB_REQUIRE(z_gathered_d, QTIP_E_ARG, "qtip_gathered_products: null pointer");
+  const unsigned char* b = static_cast<const unsigned char*>(ex->base[ex->rank]);
+  *z_gathered_d = reinterpret_cast<const float*>(b + 256 + size_t(slot) * tp_slot_bytes(ex->bytes));
   return QTIP_OK;
 }
 extern "C" int qtip_tp_status(const qtip_tp_exchange* ex, void* stream) {

@@ -80,9 +80,15 @@ class Exchange:
         self.uses += 1
         return slot
 
-    def multiply_push(self, w_shard, rotated, slot, out_full, row0, splits=1, tokens=1):
+    def multiply_push(self, w_shard, rotated, slot, out_full, row0, splits=1, tokens=1, wait=False):
+        """wait=True: the push kernel's last CTA also waits for the peers (every rank on a GPU of its own, only)."""
         lib().call("qtip_multiply_push", w_shard.pod, _p(rotated, torch.bfloat16), C.byref(self.pod), slot, out_full,
-                   row0, splits, _stream(), tokens)
+                   row0, splits, _stream(), tokens, int(wait))
+
+    def gathered(self, slot):
+        z = C.c_void_p()
+        lib().call("qtip_gathered_products", C.byref(self.pod), slot, C.byref(z))
+        return z.value
 
     def gather_wait(self, slot):
         """Enqueues the bounded wait for every rank's push of this slot; returns the device address of the gathered z."""
@@ -103,12 +109,13 @@ class Exchange:
             self._local = None
 
 
-def forward_tp(ex, w_full, w_shard, row0, x, y, scratch, rotated, round_z=False, splits=1, tokens=1):
+def forward_tp(ex, w_full, w_shard, row0, x, y, scratch, rotated, round_z=False, splits=1, tokens=1, wait_inside=True):
     """One tensor-parallel projection on this rank: input transform, products pushed to every rank, bounded wait for
-    the peers' products, output transform on the gathered z. Every rank ends with the full y."""
+    the peers' products (inside the push kernel, or as a kernel of its own with wait_inside=False), output transform on
+    the gathered z. Every rank ends with the full y. One process per GPU."""
     from . import linear
     slot = ex.next_slot()
     linear.qtip_prepare(w_shard, x, scratch, rotated, tokens)
-    ex.multiply_push(w_shard, rotated, slot, w_full.n_out, row0, splits, tokens)
-    z = ex.gather_wait(slot)
+    ex.multiply_push(w_shard, rotated, slot, w_full.n_out, row0, splits, tokens, wait_inside)
+    z = ex.gathered(slot) if wait_inside else ex.gather_wait(slot)
     linear.qtip_finish(w_full, z, y, scratch, round_z, splits, tokens)

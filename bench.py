@@ -680,21 +680,38 @@ def gemv_section(pkg, peaks, peak_src, rank, world):
 
     # The same projection with the gather fused into the product kernel: every rank's kernel stores its products into
     # every rank's gathered buffer over NVLink (plain peer stores), a one-warp kernel waits for the peers' flags.
-    ex = pkg.tp.Exchange.from_process_group(n_out)
+    ex = pkg.tp.Exchange.from_process_group(n_out, max_tokens=1, max_splits=4)
     y_nccl = torch.empty_like(y)
+    fused_splits = [1]
 
     def forward_fused():
-        pkg.tp.forward_tp(ex, full, shard, row0, x, y, scratch, rot)
+        pkg.tp.forward_tp(ex, full, shard, row0, x, y, scratch, rot, False, fused_splits[0])
 
     forward_tp()
     y_nccl.copy_(y)
     forward_fused()
     ex.check()
     same = bool(torch.equal(y.view(torch.int16), y_nccl.view(torch.int16)))
+    # Both variants are replayed from CUDA graphs of 20 projections (an even count: the fused exchange alternates its
+    # two slots), so that the numbers hold GPU time and not the host's launch rate.
     dist.barrier()
-    fus = _time_us(forward_tp, 50, torch)
+    try:
+        fus = _graph_us(forward_tp, 20, torch)
+        nccl_timing = "CUDA graph replay"
+    except Exception:  # a library that refuses capture: fall back to eager launches
+        torch.cuda.synchronize()
+        fus = _time_us(forward_tp, 50, torch)
+        nccl_timing = "eager launches"
     dist.barrier()
-    pus = _time_us(forward_fused, 50, torch)
+    pus = _graph_us(forward_fused, 20, torch)
+    ex.check()
+    sweep = {}
+    for sp in (2, 3, 4):  # K-splits give a small shard more work items than SMs; the output transform adds the partials
+        fused_splits[0] = sp
+        dist.barrier()
+        v = torch.tensor([_graph_us(forward_fused, 20, torch)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        sweep["splits_%d" % sp] = float(v[0])
     ex.check()
     dist.barrier()
     mus = _time_us(lambda: linear.qtip_multiply(shard, rot, z_local, rows, 1), 50, torch)
@@ -708,7 +725,9 @@ def gemv_section(pkg, peaks, peak_src, rank, world):
                 "collective": "all-gather of z fused into the product kernel: peer stores over NVLink (fp32, %d B per "
                               "rank and destination) + flag wait; forward_nccl_us is the same projection with "
                               "ncclAllGather" % (rows * 4),
-                "fused_equals_nccl_bitwise": differ == 0.0})
+                "fused_equals_nccl_bitwise": differ == 0.0, "forward_us_by_splits": sweep,
+                "forward_timing": "CUDA graph replay",
+                "forward_nccl_timing": nccl_timing})
     return res
 
 

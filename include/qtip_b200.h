@@ -226,9 +226,9 @@ int qtip_decode_fp8_matrix(const uint8_t* w_d, uint16_t* out_d, size_t elements,
  *
  * qtip_multiply_push computes this rank's products and stores every finished 32-row piece directly into the slot of ALL
  * ranks (plain peer stores, no staging copy, no collective call); the last CTA then raises this rank's flag on every
- * rank. qtip_gather_wait enqueues a one-warp kernel that waits, for at most about a second, until every rank's flag
- * shows the slot's next epoch, and returns the address of the local slot: the gathered z for qtip_finish (full matrix
- * geometry, splits as pushed). Epochs live on the device, so the calls can be captured in a CUDA graph and replayed.
+ * rank. The wait for the peers (at most about a second, until every rank's flag shows the slot's next epoch) is done by
+ * the last CTA of the push kernel itself (wait = 1) or by the one-warp kernel of qtip_gather_wait (wait = 0); the local
+ * slot then holds the gathered z for qtip_finish (full matrix geometry, splits as pushed). Epochs live on the device, so the calls can be captured in a CUDA graph and replayed.
  * Rule: consecutive uses of one exchange alternate slot 0 and 1 (also across graph replays), and every rank makes the
  * same sequence of calls. A wait that runs out raises the status word (qtip_tp_status) and leaves the context usable.
  * These entry points allocate nothing and do not synchronise the host; qtip_tp_alloc / qtip_tp_free / qtip_tp_export /
@@ -253,8 +253,11 @@ int qtip_tp_reset(const qtip_tp_exchange* ex, void* stream);
 /* Products of w_shard (rows [row0, row0 + w_shard.out) of a matrix of out_full rows) pushed to every rank. tokens <= the
  * max_tokens the exchange was sized for; rotated_d as for qtip_multiply. */
 int qtip_multiply_push(qtip_matrix w_shard, const uint16_t* rotated_d, const qtip_tp_exchange* ex, int slot, int out_full,
-                       int row0, int splits, void* stream, int tokens);
+                       int row0, int splits, void* stream, int tokens, int wait);
+/* wait = 0 above: the wait as a kernel of its own (required when several ranks share one GPU: a kernel must never wait
+ * for a kernel that is queued behind it). wait = 1: done by the push kernel's last CTA; then only ask for the address. */
 int qtip_gather_wait(const qtip_tp_exchange* ex, int slot, const float** z_gathered_d, void* stream);
+int qtip_gathered_products(const qtip_tp_exchange* ex, int slot, const float** z_gathered_d);
 /* Synchronises `stream`; QTIP_E_KERNEL if a wait of this rank ran out since the last reset. */
 int qtip_tp_status(const qtip_tp_exchange* ex, void* stream);
 

@@ -32,7 +32,7 @@ def main():
     for step in range(6):
         xb = pkg.synth.f32_to_bf16_bits((np.random.default_rng(step).standard_normal((tokens, n_in)) * 0.3).astype(np.float32))
         x = bf16_dev(xb)
-        pkg.tp.forward_tp(ex, w, shard, row0, x, y, scratch, rot, False, 1, tokens)
+        pkg.tp.forward_tp(ex, w, shard, row0, x, y, scratch, rot, False, 1, tokens, wait_inside=step % 3 != 2)
         ex.check()
         pkg.linear.qtip_prepare(w, x, scratch, rot, tokens)
         pkg.linear.qtip_multiply_batch(w, rot, z, n_out, 1, tokens)
