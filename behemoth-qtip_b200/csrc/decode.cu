@@ -52,6 +52,10 @@ extern __shared__ __align__(16) uint32_t gemm_smem_words[];
 // Decodes window u (word c << 16 | word c+1) into the four LUT words of states 4c..4c+3 from the replicated table
 // (entry e, copy l at word 32 e + l), so every lane reads its own bank. Bits above 15 of a shifted window do not reach
 // bits 6..15 of v (v + 1), which are the entry.
+// Decodes window u (word c << 16 | word c+1) into the four LUT words of states 4c..4c+3 from the replicated table
+// (entry e, copy l at word 32 e + l), so every lane reads its own bank. Bits above 15 of a shifted window do not reach
+// bits 6..15 of v (v + 1), which are the entry. (Other ways of forming the address -- mask then multiply-add, shift
+// then a three-input logic op, funnel shifts straight from the two source registers -- measured the same or slower.)
 __device__ __forceinline__ void decode_window(uint32_t u, uint32_t lane, uint32_t (&a)[4]) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
@@ -107,9 +111,7 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, const TpPush& push, i
       for (int q = 0; q < 4; ++q) acc[t][i1][q] = 0.f;
 
   // One 32x32 block: the lane's word of the four tiles, its neighbour's word, four windows, four MMAs per token group.
-  auto process = [&](uint2 own, int blk) {
-    const uint2 peer = make_uint2(__shfl_sync(0xffffffffu, own.x, (lane + 1) & 31),
-                                  __shfl_sync(0xffffffffu, own.y, (lane + 1) & 31));
+  auto process = [&](uint2 own, uint2 peer, int blk) {
     // B fragments of the block: for tile column j1 a lane needs bf16 pairs tg and tg + 4 of token g's eight pairs, i.e.
     // words tg, tg + 4, tg + 8, tg + 12 of the block's 16 words. XS: staged in that order in shared memory. Otherwise one
     // 16-byte load of words 4 tg .. 4 tg + 3 per token group and a 4 x 4 word transpose inside the quad (four shuffles).
@@ -157,7 +159,11 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, const TpPush& push, i
   auto consume = [&](const uint2(&src)[kChunk], int first) {
 #pragma unroll
     for (int q = 0; q < kChunk; ++q)
-      if (first + q < b_hi) process(src[q], first + q);
+      if (first + q < b_hi) {
+        const uint2 own = src[q];
+        process(own, make_uint2(__shfl_sync(0xffffffffu, own.x, (lane + 1) & 31),
+                                __shfl_sync(0xffffffffu, own.y, (lane + 1) & 31)), first + q);
+      }
   };
   if (b_lo < b_hi) {
     uint2 bufA[kChunk], bufB[kChunk];
@@ -251,7 +257,14 @@ __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matr
   float* red = reinterpret_cast<float*>(smem + kLutBytes);  // [32 warps][RT tokens][32 rows]
   uint32_t* xs = reinterpret_cast<uint32_t*>(smem + kLutBytes + 32 * RT * 32 * 4);
   const int tid = threadIdx.x, warp = tid >> 5;
-  for (int i = tid; i < 1024 * 32; i += kGemmThreads) lut_s[i] = w.lut[i >> 5];
+  {
+    // 32 copies of the table: each thread reads ONE entry from global memory, a warp then spreads its 32 entries with
+    // shuffles so that every store instruction writes 32 consecutive words (no bank conflicts, one load latency).
+    const uint32_t mine = w.lut[tid];
+    const int lane = tid & 31;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) lut_s[((warp << 5) + e) * 32 + lane] = __shfl_sync(0xffffffffu, mine, e);
+  }
   const uint32_t* xw = reinterpret_cast<const uint32_t*>(x) + size_t(t0) * (w.in / 2);
   if constexpr (XS) {
     for (int i = tid; i < w.in / 2; i += kGemmThreads) {
@@ -366,7 +379,6 @@ constexpr size_t kMaxSmem = 227 * 1024;
 static size_t gemm_smem(int nt, bool xs, int n_in) {
   return kLutBytes + size_t(32) * (xs ? 1 : nt * 8) * 32 * 4 + (xs ? size_t(n_in) * 2 : 0);
 }
-
 int decode_device_setup(DeviceInfo*) {
   QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                int(kMaxSmem)));
