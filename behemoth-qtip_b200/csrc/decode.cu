@@ -24,6 +24,8 @@ int hadamard_prepare(const uint16_t* x, const float* su, uint16_t* rotated, int 
 int hadamard_finish(const float* z, const float* sv, uint16_t* y, int n, int tokens, int splits, long split_stride,
                     int round_z, int ranks, cudaStream_t s);
 int hadamard_finish_b16(const uint16_t* z, const float* sv, uint16_t* y, int n, int tokens, int ranks, cudaStream_t s);
+int trellis_tc_multiply(qtip_matrix w, const uint16_t* x, float* z, int stride, int splits, int tokens, int* status,
+                        cudaStream_t s);  // trellis_tc.cu
 
 constexpr int kGemmThreads = 1024;
 constexpr int kWarpsPerItem = 8;
@@ -485,12 +487,18 @@ extern "C" int qtip_forward(qtip_matrix w, const uint16_t* x_d, uint16_t* y_d, f
 }
 extern "C" int qtip_multiply_batch(qtip_matrix w, const uint16_t* x_d, float* z_d, int stride, int splits, int tokens,
                                    void* stream, int implementation) {
-  (void)implementation;
   int rc = check_matrix(w, "qtip_multiply_batch");
   if (rc) return rc;
   QB_REQUIRE(x_d && z_d && tokens >= 1, QTIP_E_ARG, "qtip_multiply_batch: bad argument");
   QB_REQUIRE(stride >= w.out && splits >= 1 && splits <= 32 && splits <= w.in / 32, QTIP_E_GEOMETRY,
              "qtip_multiply_batch: stride = %d, splits = %d invalid for %d x %d", stride, splits, w.out, w.in);
+  // implementation: 0 = MMA-fragment kernel (16 tokens per pass), 2 = decode fused into the tcgen05 product, other
+  // values = by batch size: above 16 tokens the fused kernel reads the codes once per 256 tokens instead of once per 16.
+  const bool fused_ok = w.in % 64 == 0 && w.out % 128 == 0 && reinterpret_cast<uintptr_t>(x_d) % 16 == 0;
+  if (implementation == 2 || (implementation != 0 && tokens > 16 && fused_ok)) {
+    if (!device_info()) return QTIP_E_DEVICE;
+    return trellis_tc_multiply(w, x_d, z_d, stride, splits, tokens, nullptr, as_stream(stream));
+  }
   return multiply_impl<false>(w, x_d, z_d, stride, splits, tokens, as_stream(stream));
 }
 extern "C" int qtip_decode_matrix(qtip_matrix w, uint16_t* out_d, void* stream) {

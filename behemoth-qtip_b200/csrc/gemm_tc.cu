@@ -16,9 +16,7 @@
 // Warp 1 also allocates and frees the 512 TMEM columns. No TMA multicast, no peer memory. Every mbarrier wait is bounded:
 // on a time-out the CTA raises a flag in shared memory and in the caller's status word, all roles fall through, TMEM is
 // freed and the kernel returns (the result is then invalid and the host reports QTIP_E_KERNEL).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace qb {
 
@@ -26,7 +24,6 @@ constexpr int kTcM = 128, kTcN = 256, kTcK = 64, kTcStages = 3;
 constexpr int kTcHalves = 2;  // 128-row accumulators per CTA (out must be a multiple of 128; a last odd half is skipped)
 constexpr int kTcThreads = 192;
 constexpr uint32_t kTcABytes = kTcHalves * kTcM * kTcK * 2, kTcBBytes = kTcN * kTcK * 2;  // 32 KiB + 32 KiB per stage
-constexpr long long kTcWaitCycles = 2000000000LL;
 
 struct TcSmem {
   unsigned long long full[kTcStages], empty[kTcStages], acc_full;
@@ -34,71 +31,6 @@ struct TcSmem {
   int abort_flag;
 };
 constexpr size_t kTcSmemBytes = 1024 /*alignment slack*/ + size_t(kTcStages) * (kTcABytes + kTcBBytes) + sizeof(TcSmem);
-
-__device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void tc_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool tc_mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Returns false if the wait was abandoned (time-out here or elsewhere in the CTA).
-__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-  if (tc_mbar_try(bar, parity)) return true;
-  const long long start = clock64();
-  for (;;) {
-#pragma unroll 1
-    for (int spin = 0; spin < 128; ++spin)
-      if (tc_mbar_try(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - start > kTcWaitCycles) {
-      *abort_flag = 1;
-      if (status) atomicExch(status, 2);
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ void tc_tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the 128-byte swizzle:
-// 8-row groups 1,024 bytes apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= uint64_t((addr & 0x3ffffu) >> 4);       // start address, 16-byte units
-  d |= uint64_t(1) << 16;                      // leading byte offset: unused for swizzled K-major tiles
-  d |= uint64_t(1024 >> 4) << 32;              // stride byte offset
-  d |= uint64_t(1) << 46;                      // descriptor version (Blackwell)
-  d |= uint64_t(2) << 61;                      // SWIZZLE_128B
-  return d;
-}
-// Instruction descriptor: D fp32, A and B bf16, both K-major, M = 128, N = 256.
-constexpr uint32_t kTcIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kTcN >> 3) << 17) | (uint32_t(kTcM >> 4) << 24);
-
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(uint32_t(accumulate))
-      : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
 
 __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
@@ -159,7 +91,7 @@ __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_kernel(const __grid_con
         const uint64_t a_desc = tc_smem_desc(a_addr + uint32_t(h) * (kTcABytes / kTcHalves));
 #pragma unroll
         for (int kk = 0; kk < kTcK / 16; ++kk)  // 16 bf16 = 32 bytes = 2 descriptor units along K inside the swizzled row
-          tc_mma(tmem + uint32_t(h * kTcN), a_desc + uint64_t(2 * kk), b_desc + uint64_t(2 * kk), kTcIdesc,
+          tc_mma(tmem + uint32_t(h * kTcN), a_desc + uint64_t(2 * kk), b_desc + uint64_t(2 * kk), tc_idesc(kTcM, kTcN),
                  k > 0 || kk > 0);
       }
       tc_commit(smem_u32(&sm.empty[s]));  // frees the stage once these MMAs have read it
@@ -218,12 +150,12 @@ static EncodeTiledFn encode_tiled() {
   return fn;
 }
 // [rows][k] bf16 row-major, box = box_rows x 64 columns, 128-byte swizzle, zero fill outside the tensor.
-static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows) {
+int tc_make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows) {
   EncodeTiledFn fn = encode_tiled();
   QB_REQUIRE(fn, QTIP_E_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {k, rows};
   const cuuint64_t strides[1] = {k * 2};
-  const cuuint32_t box[2] = {kTcK, box_rows};
+  const cuuint32_t box[2] = {64, box_rows};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -251,9 +183,9 @@ extern "C" int qtip_prefill_gemm(const uint16_t* w_dense_d, const uint16_t* x_d,
              "qtip_prefill_gemm: operands must be 16-byte aligned");
   if (!device_info()) return QTIP_E_DEVICE;
   CUtensorMap map_w, map_x;
-  int rc = make_map(&map_w, w_dense_d, uint64_t(out), uint64_t(in), kTcM);
+  int rc = tc_make_map(&map_w, w_dense_d, uint64_t(out), uint64_t(in), kTcM);
   if (rc) return rc;
-  rc = make_map(&map_x, x_d, uint64_t(tokens), uint64_t(in), kTcN);
+  rc = tc_make_map(&map_x, x_d, uint64_t(tokens), uint64_t(in), kTcN);
   if (rc) return rc;
   const dim3 grid((out / kTcM + kTcHalves - 1) / kTcHalves, (tokens + kTcN - 1) / kTcN);
   QB_REQUIRE(grid.y <= 65535, QTIP_E_GEOMETRY, "qtip_prefill_gemm: too many tokens (%d)", tokens);

@@ -139,6 +139,8 @@ extern "C" int qtip_init(void) {
   if (rc) return rc;
   rc = gemm_tc_device_setup();
   if (rc) return rc;
+  rc = trellis_tc_device_setup();
+  if (rc) return rc;
   info.ready = true;
   g_dev[dev] = info;
   return QTIP_OK;

@@ -1,0 +1,311 @@
+// Mid-size batches (17 .. a few hundred tokens): z[token][row] = sum_k What[row][k] x[token][k] with What decoded from the
+// 2-bit trellis codes INSIDE the kernel, straight into the shared-memory A operand of tcgen05.mma. No dense copy of the
+// weights is ever written: the codes are read once per 256-token tile, which is what keeps this regime on the HBM
+// roofline of the codes instead of that of bf16 weights.
+//
+// One CTA owns 128 output rows (four 32-row block-rows) x one token tile (N = 64, 128 or 256 tokens) x one K-split.
+// Per K step (64 input columns = two 32-column blocks per block-row):
+//   warps 0..15 (decoders), in G groups (4, or 2 with 256-token tiles); group g owns the K steps k = g (mod G) and
+//       stage g of the A ring, so G steps are being decoded at once and a warp meets a barrier only once per whole
+//       32 x 32 block or two. Per block: 8 bytes of codes per lane, the neighbour's words by shuffle, four windows of
+//       four states, sixteen look-ups in the 32-copy table (as the GEMV kernel), and four stmatrix.x4: the four
+//       look-ups of a window are exactly an m16n8k16 A fragment, i.e. four 8 x 8 bf16 matrices, and stmatrix writes them
+//       as 16-byte rows to the addresses the lanes name -- here the K-major, 128-byte-swizzled positions tcgen05
+//       expects (row r, 16-byte chunk c at r * 128 + ((c ^ (r & 7)) << 4)). Eight consecutive rows hit eight different
+//       chunk positions: no bank conflicts. Then fence.proxy.async (the MMA reads through the async proxy) and one
+//       arrive per warp on the stage's barrier.
+//   warp 16, one lane : TMA loads of the activation tile (N tokens x 64 columns, K-major, 128-byte swizzle, zero fill
+//       beyond the last token) into a ring of their own (deeper than the A ring), completion by mbarrier tx bytes.
+//   warp 17, one lane : four tcgen05.mma (M128 x N x K16) per step into N TMEM columns, tcgen05.commit on the "empty"
+//       barriers of the A and the B stage; after the last step a commit on "accumulator full". Warp 17 also allocates
+//       and frees TMEM.
+//   warps 0..3 again  : epilogue, tcgen05.ld of their 32 TMEM lanes, coalesced fp32 stores of z.
+// Every mbarrier wait is bounded (tc_wait): on a time-out the CTA's abort flag and the status word are raised, all
+// roles fall through, TMEM is freed and the kernel returns.
+#include "tc_common.cuh"
+
+namespace qb {
+
+constexpr int kFtRows = 128, kFtK = 64, kFtDecoders = 16, kFtThreads = (kFtDecoders + 2) * 32;
+constexpr uint32_t kFtABytes = kFtRows * kFtK * 2;  // 16 KiB per stage
+constexpr int kFtLutBytes = 1024 * 32 * 4;         // 32 copies of the table
+constexpr int kFtMaxStages = 8;
+
+// Two rings with their own depths: the decoded A tiles come from registers (the codes are prefetched there), so two or
+// three stages decouple the decoders from the MMA; the activation tiles come from global memory through TMA and need
+// enough stages in flight to cover that latency (about 2,500 cycles against 300..500 cycles per K step).
+struct FtSmem {
+  unsigned long long full_a[kFtMaxStages], empty_a[kFtMaxStages], full_b[kFtMaxStages], empty_b[kFtMaxStages], acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+static int ft_stages_a(int n_tile) { return n_tile <= 128 ? 4 : 2; }                      // = decoder groups
+static int ft_stages_b(int n_tile) { return n_tile <= 64 ? 4 : 2; }                       // 96 KiB of stages in all
+static size_t ft_smem(int n_tile) {
+  return 1024 + kFtLutBytes + size_t(ft_stages_a(n_tile)) * kFtABytes +
+         size_t(ft_stages_b(n_tile)) * size_t(n_tile) * kFtK * 2 + sizeof(FtSmem);
+}
+
+__device__ int g_ft_status;  // used when the caller passes no status word
+
+extern __shared__ __align__(16) unsigned char ft_smem_raw[];
+
+__device__ __forceinline__ void stmatrix_x4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2),
+               "r"(r3)
+               : "memory");
+}
+
+// grid = (out / 128, token tiles, splits). z[(split * tokens + token) * stride + row]. G = decoder groups = A stages.
+template <int G>
+__global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w, const __grid_constant__ CUtensorMap map_x,
+                                                                   float* __restrict__ z, int stride, int tokens, int n_tile,
+                                                                   int stages_b, int splits,
+                                                                   int* __restrict__ status) {
+  const uint32_t raw = smem_u32(ft_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1,024-byte alignment
+  unsigned char* smem = ft_smem_raw + (base - raw);
+  uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem);
+  constexpr int stages_a = G;
+  const uint32_t a_ring = base + kFtLutBytes, b_ring = a_ring + uint32_t(stages_a) * kFtABytes;
+  const uint32_t b_bytes = uint32_t(n_tile) * kFtK * 2;
+  FtSmem& sm = *reinterpret_cast<FtSmem*>(smem + kFtLutBytes + size_t(stages_a) * kFtABytes + size_t(stages_b) * b_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * kFtRows, tok0 = blockIdx.y * n_tile, split = blockIdx.z;
+  const int k_total = w.in / kFtK;
+  const int ks_lo = int(long(k_total) * split / splits), ks_hi = int(long(k_total) * (split + 1) / splits);
+  const int k_steps = ks_hi - ks_lo;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kFtMaxStages; ++s) {
+      tc_mbar_init(smem_u32(&sm.full_a[s]), kFtDecoders / G);
+      tc_mbar_init(smem_u32(&sm.empty_a[s]), 1);
+      tc_mbar_init(smem_u32(&sm.full_b[s]), 1);
+      tc_mbar_init(smem_u32(&sm.empty_b[s]), 1);
+    }
+    tc_mbar_init(smem_u32(&sm.acc_full), 1);
+    sm.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kFtDecoders + 1) {  // TMEM allocation: whole warp, n_tile columns (a power of two >= 32)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(uint32_t(n_tile))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp < kFtDecoders) {
+    // 32 copies of the table: each decoder thread reads two entries, the warp spreads them with shuffles so that every
+    // store instruction writes 32 consecutive words.
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int e0 = (warp * 2 + h) * 32;
+      const uint32_t mine = w.lut[e0 + lane];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) lut_s[(e0 + e) * 32 + lane] = __shfl_sync(0xffffffffu, mine, e);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp < kFtDecoders) {
+    // ---- decoders: G groups of 16 / G warps; group g decodes the K steps k = g (mod G) into stage g of the A ring, so
+    // G steps are in the making at any time and a warp meets a barrier once per G / 2 whole 32 x 32 blocks.
+    constexpr int kWpg = kFtDecoders / G, kBpw = 8 / kWpg;  // warps per group, blocks per warp and step (G / 2)
+    const int grp = warp / kWpg, mem = warp % kWpg;
+    const int n2 = w.in / 32;
+    const uint32_t a_tile = a_ring + uint32_t(grp) * kFtABytes;
+    // stmatrix row addresses of this lane inside a 16 x 16 tile: matrix q = lane >> 3 (q & 1: rows + 8, q >> 1:
+    // columns + 8), row lane & 7
+    const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8, lchunk = lane >> 4;
+    const uint2* codes[kBpw];
+    int brl[kBpw], kbl[kBpw];
+#pragma unroll
+    for (int i = 0; i < kBpw; ++i) {
+      const int blk = mem * kBpw + i;  // block of the step: block-row blk >> 1, column block blk & 1
+      brl[i] = blk >> 1, kbl[i] = blk & 1;
+      codes[i] = reinterpret_cast<const uint2*>(w.trellis) + (size_t(row0 / 32 + brl[i]) * n2 + kbl[i]) * 32 + lane;
+    }
+    constexpr int kAhead = 4;  // group steps of codes in flight per lane (= 4 G K steps)
+    uint2 next[kAhead][kBpw];
+    const int first = ks_lo + grp;
+#pragma unroll
+    for (int q = 0; q < kAhead; ++q)
+#pragma unroll
+      for (int i = 0; i < kBpw; ++i) next[q][i] = codes[i][size_t(min(first + q * G, ks_hi - 1)) * 64];
+    bool ok = true;
+    for (int k0 = grp; k0 < k_steps && ok; k0 += kAhead * G) {
+#pragma unroll
+      for (int q = 0; q < kAhead; ++q) {
+        const int kk = k0 + q * G;  // K step relative to ks_lo
+        if (kk >= k_steps) break;
+        uint2 own[kBpw];
+#pragma unroll
+        for (int i = 0; i < kBpw; ++i) {
+          own[i] = next[q][i];
+          next[q][i] = codes[i][size_t(min(ks_lo + kk + kAhead * G, ks_hi - 1)) * 64];
+        }
+        if (kk >= G && !tc_wait(smem_u32(&sm.empty_a[grp]), uint32_t((kk / G - 1) & 1), abort_flag, status)) {
+          ok = false;
+          break;
+        }
+#pragma unroll
+        for (int i = 0; i < kBpw; ++i) {
+          const uint2 peer = make_uint2(__shfl_sync(0xffffffffu, own[i].x, (lane + 1) & 31),
+                                        __shfl_sync(0xffffffffu, own[i].y, (lane + 1) & 31));
+#pragma unroll
+          for (int j1 = 0; j1 < 2; ++j1) {
+            const uint32_t o = j1 ? own[i].y : own[i].x, pw = j1 ? peer.y : peer.x;
+#pragma unroll
+            for (int i1 = 0; i1 < 2; ++i1) {
+              const uint32_t u = __byte_perm(o, pw, i1 ? 0x3276 : 0x1054);  // word c << 16 | word c + 1
+              uint32_t a[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                const uint32_t v = u >> (16 - 4 * t);
+                const uint32_t y = v * v + v;
+                a[t] = lut_s[((y >> 6) & 1023u) * 32u + lane];
+              }
+              const int r = brl[i] * 32 + i1 * 16 + lrow, ch = kbl[i] * 4 + j1 * 2 + lchunk;
+              stmatrix_x4(a_tile + uint32_t(r) * 128u + (uint32_t(ch ^ (r & 7)) << 4), a[0], a[1], a[2], a[3]);
+            }
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) tc_mbar_arrive(smem_u32(&sm.full_a[grp]));
+      }
+    }
+  } else if (warp == kFtDecoders) {
+    // ---- TMA producer of the activation tiles
+    if (lane == 0) {
+      for (int k = 0; k < k_steps; ++k) {
+        const int s = k % stages_b;
+        if (k >= stages_b && !tc_wait(smem_u32(&sm.empty_b[s]), uint32_t((k / stages_b - 1) & 1), abort_flag, status))
+          break;
+        const uint32_t bar = smem_u32(&sm.full_b[s]);
+        tc_mbar_expect_tx(bar, b_bytes);
+        tc_tma_load_2d(b_ring + uint32_t(s) * b_bytes, &map_x, (ks_lo + k) * kFtK, tok0, bar);
+      }
+    }
+  } else if (lane == 0) {
+    // ---- MMA issuer
+    const uint32_t idesc = tc_idesc(kFtRows, n_tile);
+    bool ok = true;
+    for (int k = 0; k < k_steps && ok; ++k) {
+      const int sa = k % stages_a, sb = k % stages_b;
+      ok = tc_wait(smem_u32(&sm.full_b[sb]), uint32_t((k / stages_b) & 1), abort_flag, status) &&
+           tc_wait(smem_u32(&sm.full_a[sa]), uint32_t((k / stages_a) & 1), abort_flag, status);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint64_t a_desc = tc_smem_desc(a_ring + uint32_t(sa) * kFtABytes);
+      const uint64_t b_desc = tc_smem_desc(b_ring + uint32_t(sb) * b_bytes);
+#pragma unroll
+      for (int kk = 0; kk < kFtK / 16; ++kk)
+        tc_mma(tmem, a_desc + uint64_t(2 * kk), b_desc + uint64_t(2 * kk), idesc, k > 0 || kk > 0);
+      tc_commit(smem_u32(&sm.empty_a[sa]));  // each commit tracks all MMAs issued so far
+      tc_commit(smem_u32(&sm.empty_b[sb]));
+    }
+    if (ok) tc_commit(smem_u32(&sm.acc_full));
+  }
+
+  if (warp < 4) {
+    // ---- epilogue: warp q reads TMEM lanes 32 q .. 32 q + 31 (rows), columns = tokens of the tile
+    const bool ok = k_steps > 0 && tc_wait(smem_u32(&sm.acc_full), 0, abort_flag, status);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int row = row0 + warp * 32 + lane;
+    float* zs = z + size_t(split) * tokens * stride + row;
+#pragma unroll 1
+    for (int cc = 0; cc < n_tile; cc += 32) {
+      if (tok0 + cc >= tokens) break;
+      uint32_t v[32];
+      if (ok) {
+        const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16) + uint32_t(cc);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = 0u;  // an empty K range (more splits than K steps) contributes zeros
+      }
+      if (ok || k_steps == 0) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int tok = tok0 + cc + c;
+          if (tok < tokens) zs[size_t(tok) * stride] = __uint_as_float(v[c]);
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == kFtDecoders + 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(n_tile)) : "memory");
+  }
+}
+
+int trellis_tc_device_setup() {
+  QB_CUDA(cudaFuncSetAttribute(trellis_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ft_smem(256))));
+  QB_CUDA(cudaFuncSetAttribute(trellis_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ft_smem(64))));
+  return QTIP_OK;
+}
+
+// Token tile of the fused kernel for a batch: the smallest of 64 / 128 / 256 that holds it, else 256.
+static int ft_token_tile(int tokens) { return tokens <= 64 ? 64 : (tokens <= 128 ? 128 : 256); }
+
+int trellis_tc_multiply(qtip_matrix w, const uint16_t* x, float* z, int stride, int splits, int tokens, int* status,
+                        cudaStream_t s) {
+  QB_REQUIRE(w.in % kFtK == 0 && w.out % kFtRows == 0, QTIP_E_GEOMETRY,
+             "the fused tensor-core product needs in %% 64 == 0 and out %% 128 == 0 (in = %d, out = %d)", w.in, w.out);
+  QB_REQUIRE(reinterpret_cast<uintptr_t>(x) % 16 == 0, QTIP_E_ARG, "activations must be 16-byte aligned");
+  const int n_tile = ft_token_tile(tokens);
+  CUtensorMap map_x;
+  int rc = tc_make_map(&map_x, x, uint64_t(tokens), uint64_t(w.in), uint32_t(n_tile));
+  if (rc) return rc;
+  if (!status) {
+    void* p = nullptr;
+    QB_CUDA(cudaGetSymbolAddress(&p, g_ft_status));
+    status = static_cast<int*>(p);
+  }
+  const dim3 grid(w.out / kFtRows, (tokens + n_tile - 1) / n_tile, splits);
+  QB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, QTIP_E_GEOMETRY, "too many token tiles or splits");
+  if (ft_stages_a(n_tile) == 4)
+    trellis_tc_kernel<4><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile,
+                                                                   ft_stages_b(n_tile), splits, status);
+  else
+    trellis_tc_kernel<2><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile,
+                                                                   ft_stages_b(n_tile), splits, status);
+  QB_LAUNCHED();
+  return QTIP_OK;
+}
+
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" int qtip_multiply_tc(qtip_matrix w, const uint16_t* rotated_d, float* z_d, int stride, int splits, int tokens,
+                                int* status_d, void* stream) {
+  QB_REQUIRE(w.trellis && w.lut && rotated_d && z_d && tokens >= 1, QTIP_E_ARG, "qtip_multiply_tc: bad argument");
+  QB_REQUIRE(w.in > 0 && w.out > 0 && stride >= w.out && splits >= 1 && splits <= 32, QTIP_E_GEOMETRY,
+             "qtip_multiply_tc: stride = %d, splits = %d invalid for %d x %d", stride, splits, w.out, w.in);
+  if (!device_info()) return QTIP_E_DEVICE;
+  return trellis_tc_multiply(w, rotated_d, z_d, stride, splits, tokens, status_d, as_stream(stream));
+}
+extern "C" int qtip_kernel_status(void* stream) {
+  int h = 0;
+  QB_CUDA(cudaMemcpyFromSymbolAsync(&h, g_ft_status, sizeof h, 0, cudaMemcpyDeviceToHost, as_stream(stream)));
+  QB_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  QB_REQUIRE(h == 0, QTIP_E_KERNEL, "a bounded pipeline wait of a tensor-core kernel ran out (status %d)", h);
+  return QTIP_OK;
+}

@@ -80,6 +80,25 @@ def qtip_multiply_batch(w, x, z, stride, splits, tokens, implementation=-1):
                _stream(), implementation)
 
 
+def qtip_multiply_tc(w, x, z, stride, splits, tokens, status=None):
+    """Decode fused into the tcgen05 product (17 .. a few hundred tokens); z [splits, tokens, stride] fp32."""
+    init()
+    lib().call("qtip_multiply_tc", w.pod, _p(x, torch.bfloat16), _p(z, torch.float32), stride, splits, tokens,
+               _p(status, torch.int32), _stream())
+
+
+def tc_splits(n_out, sm_count=148, max_splits=4):
+    """K-splits for qtip_multiply_tc that waste the fewest SM rounds: the kernel runs out / 128 x splits CTAs of
+    1 / splits of the K range each, one per SM at a time."""
+    tiles = max(1, n_out // 128)
+    return min(range(1, max_splits + 1), key=lambda sp: (-(-tiles * sp // sm_count) / sp, sp))
+
+
+def kernel_status():
+    """Synchronises; raises QtipError if a tensor-core kernel without a status word reported a time-out."""
+    lib().call("qtip_kernel_status", _stream())
+
+
 def qtip_decode_matrix(w, out):
     init()
     lib().call("qtip_decode_matrix", w.pod, _p(out, torch.bfloat16), _stream())

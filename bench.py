@@ -530,8 +530,9 @@ def ldlq_workload(args):
 def layer_workload(args):
     """Decode/prefill products of one Mistral-Large-shaped layer (hidden 12288, intermediate 28672, 96 Q / 8 KV heads of
     128): q, o, gate, up, down as 2-bit QTIP linears with random codes, k, v as FP8 e4m3, bf16 activations N(0,1), token
-    batches 1, 16, 64 and 2048. Each linear runs input transform, product, output transform. <= 64 tokens: MMA-fragment
-    kernel (HBM-side metric: code bytes per second); 2048 tokens: dense decode + tcgen05 GEMM (TFLOP/s). One GPU."""
+    batches 1, 16, 64, 256 and 2048. Each linear runs input transform, product, output transform. <= 16 tokens:
+    MMA-fragment kernel; 64 and 256 tokens: decode fused into the tcgen05 product (HBM-side metric: code bytes per
+    second); 2048 tokens: dense decode + tcgen05 GEMM (TFLOP/s). One GPU."""
     import torch
     import __graft_entry__ as graft
     pkg = graft.load_package()
@@ -560,20 +561,23 @@ def layer_workload(args):
     dense = torch.empty(inter * hidden, dtype=torch.bfloat16, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     out = {}
-    for T in (1, 16, 64, 2048):
+    for T in (1, 16, 64, 256, 2048):
         g.manual_seed(10)
         xs = {n: torch.randn(T, n, generator=g, device="cuda").to(torch.bfloat16) for n in (hidden, inter)}
         rot = {n: torch.empty(T, n, dtype=torch.bfloat16, device="cuda") for n in (hidden, inter)}
         ys = {n: torch.empty(T, n, dtype=torch.bfloat16, device="cuda") for n in (hidden, inter, kv)}
-        splits = {name: (2 if (T <= 64 and shapes[name][1] == hidden) else 1) for name in shapes}
-        z = torch.empty(2 * T * inter, dtype=torch.float32, device="cuda")
+        if 16 < T <= 512:
+            splits = {name: linear.tc_splits(shapes[name][1]) for name in shapes}
+        else:
+            splits = {name: (2 if (T <= 16 and shapes[name][1] == hidden) else 1) for name in shapes}
+        z = torch.empty(4 * T * inter if T <= 512 else T * inter, dtype=torch.float32, device="cuda")
         scratch = torch.empty(1, dtype=torch.float32, device="cuda")
 
         def layer():
             for name, (n_in, n_out) in shapes.items():
                 w, sp = mats[name], splits[name]
                 linear.qtip_prepare(w, xs[n_in], scratch, rot[n_in], T)
-                if T >= 128:
+                if T > 512:
                     linear.qtip_multiply_prefill(w, rot[n_in], z, n_out, T, dense[:n_out * n_in].view(n_out, n_in), status)
                 elif T == 1:
                     linear.qtip_multiply(w, rot[n_in], z, n_out, sp, 1)
@@ -586,13 +590,14 @@ def layer_workload(args):
                 else:
                     linear.fp8_forward(w, s8, xs[hidden], ys[kv], hidden, kv, T)
 
-        us = _graph_us(layer, 2, torch) if T <= 64 else _time_us(layer, 3, torch)
+        us = _graph_us(layer, 2, torch) if T <= 512 else _time_us(layer, 3, torch)
         flops = 2.0 * T * weights
         out["T%d" % T] = {"layer_us": us, "code_gbs": code_bytes / us / 1e3, "tflops": flops / us / 1e6,
                           "frac_of_hbm_peak": code_bytes / us / 1e3 / peaks["hbm_gbs"],
                           "frac_of_bf16_peak": flops / us / 1e6 / peaks["bf16_tflops"]}
         del xs, rot, ys, z
     assert int(status) == 0
+    linear.kernel_status()
     print(json.dumps({"metric": "qtip_layer_products", "unit": "us per layer", "n_gpus": 1, "data": "synthetic",
                       "config": {"workload": "mistral_large_layer_products", "hidden": hidden, "intermediate": inter,
                                  "code_bytes": code_bytes, "weights": weights, "peaks": peak_src}, "tokens": out}))

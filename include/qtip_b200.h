@@ -204,6 +204,19 @@ int qtip_reduce_to_b16(const float* x_d, const float* scale_d, uint16_t* y_d, si
 int qtip_prefill_gemm(const uint16_t* w_dense_d, const uint16_t* x_d, float* z_d, int stride, int in, int out, int tokens,
                       int* status_d, void* stream);
 
+/* Products for 17 .. a few hundred tokens with the decode fused into the tcgen05 product: the codes are decoded straight
+ * into the shared-memory A operand (no dense copy of the weights), 128 rows x 64/128/256 tokens per CTA, K split
+ * `splits` ways (z_d[(split * tokens + token) * stride + row], summed by qtip_finish / qtip_reduce_products). Needs
+ * in % 64 == 0 and out % 128 == 0. status_d (one int, may be NULL: then a word inside the library, read by
+ * qtip_kernel_status) is set to 2 if a bounded pipeline wait timed out. qtip_multiply_batch takes this path by itself
+ * above 16 tokens (implementation = 0 keeps the 16-tokens-per-pass kernel, 2 forces this one). Takes the place of the
+ * 17..127-token kernel of runtime/cuda/batch_kernels.cu:23-288 (launch<0>) and, up to a few hundred tokens, of the dense
+ * decode + library GEMM of runtime/cuda/tensor_model.cpp:210-222. */
+int qtip_multiply_tc(qtip_matrix w, const uint16_t* rotated_d, float* z_d, int stride, int splits, int tokens,
+                     int* status_d, void* stream);
+/* Synchronises `stream`; QTIP_E_KERNEL if a tensor-core kernel launched without a status word reported a time-out. */
+int qtip_kernel_status(void* stream);
+
 /* FP8 (e4m3) W8A16 projection of the K/V weights kept beside the QTIP linears: y[t][o] = bf16((sum_i fp8(w[o][i]) *
  * bf16(x[t][i])) * scale[o]), fp32 accumulation. w_d [out][in] bytes, scale_d [out], x_d [tokens][in] bf16, y_d
  * [tokens][out] bf16. runtime/cuda/kernels.cu:279-289,477-480 (fp8_forward) and batch_kernels.cu:750-763

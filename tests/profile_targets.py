@@ -2,6 +2,8 @@
 
     python tests/profile_targets.py viterbi <sequences>     # 4 forward passes of the cluster Viterbi kernel
     python tests/profile_targets.py gemv <out rows>         # 3 x qtip_forward on an <out rows> x 12288 linear
+    python tests/profile_targets.py fused <out rows> [tokens] [splits]   # 3 x qtip_multiply_tc, <out rows> x 12288
+    python tests/profile_targets.py prefill <out rows> [tokens]          # 3 x qtip_prefill_gemm, <out rows> x 12288
 """
 import os
 import sys
@@ -27,6 +29,33 @@ def main():
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
         for _ in range(4):
             codec.k_viterbi_fwd_words(X, None, 1, size, bp, 0, fs, lut_d, status)
+        torch.cuda.synchronize()
+        assert int(status) == 0
+    elif what == "prefill":
+        n_in, n_out = 12288, size
+        tokens = int(sys.argv[3]) if len(sys.argv) > 3 else 2048
+        wd = torch.randn(n_out, n_in, generator=gen, device="cuda").to(torch.bfloat16)
+        x = torch.randn(tokens, n_in, generator=gen, device="cuda").to(torch.bfloat16)
+        z = torch.empty((tokens, n_out), dtype=torch.float32, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for _ in range(3):
+            linear.prefill_gemm(wd, x, z, n_out, n_in, n_out, tokens, status)
+        torch.cuda.synchronize()
+        assert int(status) == 0
+    elif what == "fused":
+        n_in, n_out = 12288, size
+        tokens = int(sys.argv[3]) if len(sys.argv) > 3 else 64
+        splits = int(sys.argv[4]) if len(sys.argv) > 4 else 1
+        trellis = torch.randint(-32768, 32768, ((n_out // 16) * (n_in // 16) * 32,), generator=gen, device="cuda",
+                                dtype=torch.int16)
+        su = torch.from_numpy(synth.signs(n_in, 7)).cuda()
+        sv = torch.from_numpy(synth.signs(n_out, 8)).cuda()
+        w = linear.Matrix(trellis, su, sv, linear.runtime_lut(synth.seeded_tlut(1)), n_in, n_out)
+        x = torch.randn(tokens, n_in, generator=gen, device="cuda").to(torch.bfloat16)
+        z = torch.empty((splits, tokens, n_out), dtype=torch.float32, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for _ in range(3):
+            linear.qtip_multiply_tc(w, x, z, n_out, splits, tokens, status)
         torch.cuda.synchronize()
         assert int(status) == 0
     else:

@@ -212,3 +212,30 @@ def test_multiply_prefill_matches_batch_path(gpu, oracle):
     W = oracle.decode_rows(tr, n_in, n_out, tl, 0, n_out, True).astype(np.float64)
     ref = gpu.synth.bf16_bits_to_f32(xb).astype(np.float64) @ W.T
     assert rel_l2(z.cpu().numpy(), ref) < 1e-5
+
+
+@pytest.mark.parametrize("n_in,n_out,tokens,splits", [(1024, 256, 17, 1), (1024, 256, 64, 2), (1024, 384, 100, 1),
+                                                      (3584, 128, 128, 3), (2048, 256, 200, 1), (1024, 256, 256, 1),
+                                                      (1024, 256, 300, 2), (12288, 512, 40, 1), (64, 128, 33, 4)])
+def test_fused_decode_tensor_core_product(gpu, oracle, n_in, n_out, tokens, splits):
+    """Decode fused into the tcgen05 product against float64 on the bit-exact decoded weights: only the fp32 summation
+    order differs, rel-L2 <= 5e-5 (K up to 12,288). Token tiles of 64 / 128 / 256 incl. ragged ends, K-splits incl.
+    more splits than K steps, and the deterministic repeat."""
+    w, tr, su, sv, tl = make_linear(gpu, n_in, n_out, 700 + tokens)
+    xb = gpu.synth.f32_to_bf16_bits(np.random.default_rng(tokens).standard_normal((tokens, n_in)).astype(np.float32))
+    z = torch.full((splits, tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gpu.linear.qtip_multiply_tc(w, bf16_dev(xb), z, n_out, splits, tokens, status)
+    assert int(status) == 0
+    W = oracle.decode_rows(tr, n_in, n_out, tl, 0, n_out, True).astype(np.float64)
+    ref = gpu.synth.bf16_bits_to_f32(xb).astype(np.float64) @ W.T
+    got = z.sum(0).cpu().numpy()
+    assert np.isfinite(got).all()
+    assert rel_l2(got, ref) < 5e-5
+    z2 = torch.zeros_like(z)
+    if splits <= n_in // 32:  # the batch entry point keeps the reference's bound on K-splits
+        gpu.linear.qtip_multiply_batch(w, bf16_dev(xb), z2, n_out, splits, tokens, 2)
+        gpu.linear.kernel_status()
+    else:
+        gpu.linear.qtip_multiply_tc(w, bf16_dev(xb), z2, n_out, splits, tokens, status)
+    assert torch.equal(z, z2)
