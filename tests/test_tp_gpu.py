@@ -28,7 +28,7 @@ def sharded_reference(gpu, w, x, ranks, splits, tokens, round_z):
     z = torch.zeros((splits, tokens, n_out), dtype=torch.float32, device="cuda")
     for r in range(ranks):
         zl = torch.zeros((splits, tokens, rows), dtype=torch.float32, device="cuda")
-        lin.qtip_multiply_batch(w.rows(r * rows, rows), rot, zl, rows, splits, tokens)
+        lin.qtip_multiply_batch(w.rows(r * rows, rows), rot, zl, rows, splits, tokens, 0)  # the kernel the push uses
         z[:, :, r * rows:(r + 1) * rows] = zl
     y = torch.empty((tokens, n_out), dtype=torch.bfloat16, device="cuda")
     lin.qtip_finish(w, z, y, scratch, round_z, splits, tokens)
