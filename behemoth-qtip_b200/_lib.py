@@ -60,6 +60,8 @@ SIGNATURES = {
     "qtip_k_viterbi_finish_words": [_P, _P, _I, _I, _P, _I, _I, _P, _P, _L, _I, _P, _P],
     "qtip_tiles_from_matrix": [_P, _L, _L, _L, _P, _P],
     "qtip_ldlq": [_P, _P, _L, _L, _L, _L, _P, _P, _P, _P, _Z, _P],
+    "qtip_quantize_linear": [_P, _P, _L, _L, _P, _P, _P, C.c_double, C.c_double, _P, _P, _P, _P, C.POINTER(C.c_float), _P,
+                             _Z, _P],
     "qtip_pack_trellis": [_P, _L, _P, _P],
     "qtip_unpack_trellis": [_P, _L, _P, _P],
     "qtip_swizzle_for_kernel": [_P, _I, _I, _P, _P],
@@ -94,6 +96,7 @@ _RESTYPES = {
     "qtip_abi_version": (C.c_int, []),
     "qtip_quantize_workspace_bytes": (C.c_size_t, [_I]),
     "qtip_ldlq_workspace_bytes": (C.c_size_t, [_L, _L]),
+    "qtip_quantize_linear_workspace_bytes": (C.c_size_t, [_L, _L]),
     "qtip_tp_exchange_bytes": (C.c_size_t, [_I, _I, _I]),
 }
 

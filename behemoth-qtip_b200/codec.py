@@ -335,3 +335,22 @@ def quantize_linear(W, L, su, sv, lut_h2, lut_rms, workspace=None, scale_overrid
     trellis = swizzle_for_kernel(packed, m, n)
     return {"trellis": trellis, "SU": su.to(torch.bfloat16), "SV": sv * wscale, "wscale": wscale, "WT": WT,
             "hatWT": hatWT, "Q": Q, "workspace": ws}
+
+
+def quantize_linear_fused(W, L, su, sv, lut_h2, lut_rms, workspace=None, scale_override=0.9):
+    """quantize_linear as ONE C-ABI call (qtip_quantize_linear): same inputs, same outputs, bit for bit."""
+    init()
+    m, n = W.shape
+    WT = torch.empty((n, m), dtype=torch.float32, device=W.device)
+    hatWT = torch.empty_like(WT)
+    Q = torch.empty(((m // 16) * (n // 16), 128), dtype=torch.int16, device=W.device)
+    trellis = torch.empty(((m // 16) * (n // 16), 32), dtype=torch.int16, device=W.device)
+    if workspace is None:
+        workspace = Workspace(lib().raw("qtip_quantize_linear_workspace_bytes")(m, n))
+    wscale = C.c_float()
+    lib().call("qtip_quantize_linear", _p(W, torch.float32), _p(L, torch.float32), m, n, _p(su, torch.float32),
+               _p(sv, torch.float32), _p(lut_h2, torch.int32), float(lut_rms), float(scale_override),
+               _p(WT, torch.float32), _p(hatWT, torch.float32), _p(Q, torch.int16), _p(trellis, torch.int16),
+               C.byref(wscale), workspace.ptr, workspace.nbytes, _stream())
+    return {"trellis": trellis, "SU": su.to(torch.bfloat16), "SV": sv * wscale.value, "wscale": wscale.value, "WT": WT,
+            "hatWT": hatWT, "Q": Q, "workspace": workspace}

@@ -8,6 +8,8 @@
 //    every element is one thread's fp32 FMA chain over k ascending, which is deterministic and at least as accurate.
 //    128 x 128 output tile per CTA, 8 x 8 per thread, the 128-deep operand panels staged through shared memory.
 //  * qtip_ldlq: the schedule of ldlq_gpu (src/quantizer.cpp:30-89) on one stream, restricted to a slice of W rows.
+#include <cmath>
+
 #include "common.cuh"
 
 namespace qb {
@@ -168,4 +170,54 @@ extern "C" int qtip_ldlq(const float* WT_d, const float* L_d, long n, long m, lo
     }
   }
   return QTIP_OK;
+}
+
+// ---------------------------------------------------------------- one linear of a Hessian group, end to end
+// The per-linear body of quantize_group (src/quantizer.cpp:236-320) on one stream: random-Hadamard rotation of W on both
+// sides, Wscale from the rotated rms, LDLQ + Viterbi, bit packing and the kernel layout. Workspace:
+// [LDLQ workspace][packed words][one double].
+static size_t packed_bytes(long m, long n) { return align256(size_t(m / 16) * (n / 16) * 32 * 2); }
+
+extern "C" size_t qtip_quantize_linear_workspace_bytes(long m, long n) {
+  if (m <= 0 || n <= 0) return 0;
+  return qtip_ldlq_workspace_bytes(n, m) + packed_bytes(m, n) + 256;
+}
+
+extern "C" int qtip_quantize_linear(float* W_d, const float* L_d, long m, long n, const float* su_d, const float* sv_d,
+                                    const uint32_t* lut_h2_d, double lut_rms, double scale_override, float* WT_d,
+                                    float* hatWT_d, uint16_t* Q_d, uint16_t* trellis_d, float* wscale_out,
+                                    void* workspace_d, size_t workspace_bytes, void* stream) {
+  QB_REQUIRE(W_d && L_d && su_d && sv_d && lut_h2_d && WT_d && hatWT_d && Q_d && trellis_d && wscale_out && workspace_d,
+             QTIP_E_ARG, "qtip_quantize_linear: null pointer");
+  QB_REQUIRE(m > 0 && n > 0 && m % 32 == 0 && n % 128 == 0, QTIP_E_GEOMETRY,
+             "qtip_quantize_linear needs m %% 32 == 0 and n %% 128 == 0 (m = %ld, n = %ld)", m, n);
+  QB_REQUIRE(lut_rms > 0 && scale_override > 0, QTIP_E_ARG, "qtip_quantize_linear: lut_rms and scale_override must be > 0");
+  const size_t ldlq_bytes = qtip_ldlq_workspace_bytes(n, m), pk_bytes = packed_bytes(m, n);
+  QB_REQUIRE(workspace_bytes >= ldlq_bytes + pk_bytes + 256, QTIP_E_WORKSPACE,
+             "qtip_quantize_linear: workspace of %zu bytes is too small (need %zu)", workspace_bytes,
+             ldlq_bytes + pk_bytes + 256);
+  unsigned char* p = static_cast<unsigned char*>(workspace_d);
+  uint16_t* packed = reinterpret_cast<uint16_t*>(p + ldlq_bytes);
+  double* acc = reinterpret_cast<double*>(p + ldlq_bytes + pk_bytes);
+  cudaStream_t s = as_stream(stream);
+  int rc;
+  // Wr = T_m^T diag(SV) W diag(SU) T_n, kept transposed (n x m) for the column-wise LDLQ
+  if ((rc = qtip_k_scale_rows_cols(W_d, m, n, n, sv_d, su_d, stream))) return rc;
+  if ((rc = qtip_k_hadamard_rows(W_d, m, int(n), n, 1, stream))) return rc;
+  if ((rc = qtip_k_transpose(W_d, m, n, n, WT_d, m, stream))) return rc;
+  if ((rc = qtip_k_hadamard_rows(WT_d, n, int(m), m, 1, stream))) return rc;
+  QB_CUDA(cudaMemsetAsync(acc, 0, sizeof(double), s));
+  if ((rc = qtip_k_sumsq(WT_d, n, m, m, acc, stream))) return rc;
+  double sumsq = 0;
+  QB_CUDA(cudaMemcpyAsync(&sumsq, acc, sizeof sumsq, cudaMemcpyDeviceToHost, s));
+  QB_CUDA(cudaStreamSynchronize(s));  // the reference reads the rms back at the same point
+  const double rms = std::sqrt(sumsq / (double(n) * double(m)));
+  const float wscale = float(rms / (double(float(lut_rms)) * scale_override));
+  QB_REQUIRE(wscale > 0 && std::isfinite(wscale), QTIP_E_ARG, "qtip_quantize_linear: the rotated weights have rms %g", rms);
+  *wscale_out = wscale;
+  if ((rc = qtip_k_scale(WT_d, n, m, m, float(1.0 / double(wscale)), stream))) return rc;
+  if ((rc = qtip_ldlq(WT_d, L_d, n, m, 0, m, hatWT_d, Q_d, lut_h2_d, workspace_d, ldlq_bytes, stream))) return rc;
+  const long tiles = (m / 16) * (n / 16);
+  if ((rc = qtip_pack_trellis(Q_d, tiles, packed, stream))) return rc;
+  return qtip_swizzle_for_kernel(packed, int(m), int(n), trellis_d, stream);
 }

@@ -31,45 +31,44 @@ constexpr uint32_t kFtABytes = kFtRows * kFtK * 2;  // 16 KiB per stage
 constexpr int kFtLutBytes = 1024 * 32 * 4;         // 32 copies of the table
 constexpr int kFtMaxStages = 8;
 
-// Two rings with their own depths: the decoded A tiles come from registers (the codes are prefetched there), so two or
-// three stages decouple the decoders from the MMA; the activation tiles come from global memory through TMA and need
-// enough stages in flight to cover that latency (about 2,500 cycles against 300..500 cycles per K step).
 struct FtSmem {
-  unsigned long long full_a[kFtMaxStages], empty_a[kFtMaxStages], full_b[kFtMaxStages], empty_b[kFtMaxStages], acc_full;
+  unsigned long long full[kFtMaxStages], empty[kFtMaxStages], acc_full;
   uint32_t tmem_base;
   int abort_flag;
 };
-static int ft_stages_a(int n_tile) { return n_tile <= 128 ? 4 : 2; }                      // = decoder groups
-static int ft_stages_b(int n_tile) { return n_tile <= 64 ? 4 : 2; }                       // 96 KiB of stages in all
+// One ring: a stage holds the decoded A tile and the activation tile of a K step, filled behind ONE barrier (the arrivals
+// of the group's decoder warps plus the TMA's transaction bytes) and released by ONE tcgen05.commit, so the single MMA
+// thread runs one wait and one commit per step. Stages = decoder groups: 4 (64 tokens), 2 (128 or 256 tokens).
+static int ft_stages(int n_tile) { return n_tile <= 64 ? 4 : 2; }
 static size_t ft_smem(int n_tile) {
-  return 1024 + kFtLutBytes + size_t(ft_stages_a(n_tile)) * kFtABytes +
-         size_t(ft_stages_b(n_tile)) * size_t(n_tile) * kFtK * 2 + sizeof(FtSmem);
+  return 1024 + kFtLutBytes + size_t(ft_stages(n_tile)) * (kFtABytes + size_t(n_tile) * kFtK * 2) + sizeof(FtSmem);
 }
 
 __device__ int g_ft_status;  // used when the caller passes no status word
 
 extern __shared__ __align__(16) unsigned char ft_smem_raw[];
 
+// No "memory" clobber: the stores go to the A ring only, and the compiler must stay free to issue the table look-ups of
+// the following windows before this store (a clobber would serialise look-up latency window by window). The fence and
+// the barrier arrive that follow the last store of a step are volatile with a clobber, which keeps the order that matters.
 __device__ __forceinline__ void stmatrix_x4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
   asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2),
-               "r"(r3)
-               : "memory");
+               "r"(r3));
 }
 
 // grid = (out / 128, token tiles, splits). z[(split * tokens + token) * stride + row]. G = decoder groups = A stages.
 template <int G>
 __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w, const __grid_constant__ CUtensorMap map_x,
                                                                    float* __restrict__ z, int stride, int tokens, int n_tile,
-                                                                   int stages_b, int splits,
+                                                                   int splits,
                                                                    int* __restrict__ status) {
   const uint32_t raw = smem_u32(ft_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1,024-byte alignment
   unsigned char* smem = ft_smem_raw + (base - raw);
   uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem);
-  constexpr int stages_a = G;
-  const uint32_t a_ring = base + kFtLutBytes, b_ring = a_ring + uint32_t(stages_a) * kFtABytes;
+  const uint32_t a_ring = base + kFtLutBytes, b_ring = a_ring + uint32_t(G) * kFtABytes;
   const uint32_t b_bytes = uint32_t(n_tile) * kFtK * 2;
-  FtSmem& sm = *reinterpret_cast<FtSmem*>(smem + kFtLutBytes + size_t(stages_a) * kFtABytes + size_t(stages_b) * b_bytes);
+  FtSmem& sm = *reinterpret_cast<FtSmem*>(smem + kFtLutBytes + size_t(G) * (kFtABytes + b_bytes));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = blockIdx.x * kFtRows, tok0 = blockIdx.y * n_tile, split = blockIdx.z;
   const int k_total = w.in / kFtK;
@@ -79,10 +78,8 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kFtMaxStages; ++s) {
-      tc_mbar_init(smem_u32(&sm.full_a[s]), kFtDecoders / G);
-      tc_mbar_init(smem_u32(&sm.empty_a[s]), 1);
-      tc_mbar_init(smem_u32(&sm.full_b[s]), 1);
-      tc_mbar_init(smem_u32(&sm.empty_b[s]), 1);
+      tc_mbar_init(smem_u32(&sm.full[s]), kFtDecoders / G + 1);  // the group's warps + the TMA lane (with its bytes)
+      tc_mbar_init(smem_u32(&sm.empty[s]), 1);
     }
     tc_mbar_init(smem_u32(&sm.acc_full), 1);
     sm.abort_flag = 0;
@@ -147,10 +144,11 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
           own[i] = next[q][i];
           next[q][i] = codes[i][size_t(min(ks_lo + kk + kAhead * G, ks_hi - 1)) * 64];
         }
-        if (kk >= G && !tc_wait(smem_u32(&sm.empty_a[grp]), uint32_t((kk / G - 1) & 1), abort_flag, status)) {
+        if (kk >= G && !tc_wait(smem_u32(&sm.empty[grp]), uint32_t((kk / G - 1) & 1), abort_flag, status)) {
           ok = false;
           break;
         }
+#ifndef QB_FT_NODECODE
 #pragma unroll
         for (int i = 0; i < kBpw; ++i) {
           const uint2 peer = make_uint2(__shfl_sync(0xffffffffu, own[i].x, (lane + 1) & 31),
@@ -173,21 +171,30 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
             }
           }
         }
+#else  // timing experiment only: the synchronisation skeleton without the decode work
+        if (own[0].x == 0x12345678u) stmatrix_x4(a_tile, own[0].x, own[0].y, 0, 0);
+        (void)lrow, (void)lchunk, (void)brl, (void)kbl;
+#endif
+#ifndef QB_FT_NOFENCE
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
         __syncwarp();
-        if (lane == 0) tc_mbar_arrive(smem_u32(&sm.full_a[grp]));
+        if (lane == 0) tc_mbar_arrive(smem_u32(&sm.full[grp]));
       }
     }
   } else if (warp == kFtDecoders) {
     // ---- TMA producer of the activation tiles
     if (lane == 0) {
       for (int k = 0; k < k_steps; ++k) {
-        const int s = k % stages_b;
-        if (k >= stages_b && !tc_wait(smem_u32(&sm.empty_b[s]), uint32_t((k / stages_b - 1) & 1), abort_flag, status))
-          break;
-        const uint32_t bar = smem_u32(&sm.full_b[s]);
+        const int s = k % G;
+        if (k >= G && !tc_wait(smem_u32(&sm.empty[s]), uint32_t((k / G - 1) & 1), abort_flag, status)) break;
+        const uint32_t bar = smem_u32(&sm.full[s]);
+#ifndef QB_FT_NOTMA
         tc_mbar_expect_tx(bar, b_bytes);
         tc_tma_load_2d(b_ring + uint32_t(s) * b_bytes, &map_x, (ks_lo + k) * kFtK, tok0, bar);
+#else
+        tc_mbar_arrive(bar);
+#endif
       }
     }
   } else if (lane == 0) {
@@ -195,18 +202,20 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
     const uint32_t idesc = tc_idesc(kFtRows, n_tile);
     bool ok = true;
     for (int k = 0; k < k_steps && ok; ++k) {
-      const int sa = k % stages_a, sb = k % stages_b;
-      ok = tc_wait(smem_u32(&sm.full_b[sb]), uint32_t((k / stages_b) & 1), abort_flag, status) &&
-           tc_wait(smem_u32(&sm.full_a[sa]), uint32_t((k / stages_a) & 1), abort_flag, status);
+      const int sa = k % G, sb = sa;
+      ok = tc_wait(smem_u32(&sm.full[sa]), uint32_t((k / G) & 1), abort_flag, status);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint64_t a_desc = tc_smem_desc(a_ring + uint32_t(sa) * kFtABytes);
       const uint64_t b_desc = tc_smem_desc(b_ring + uint32_t(sb) * b_bytes);
+#ifndef QB_FT_NOMMA
 #pragma unroll
       for (int kk = 0; kk < kFtK / 16; ++kk)
         tc_mma(tmem, a_desc + uint64_t(2 * kk), b_desc + uint64_t(2 * kk), idesc, k > 0 || kk > 0);
-      tc_commit(smem_u32(&sm.empty_a[sa]));  // each commit tracks all MMAs issued so far
-      tc_commit(smem_u32(&sm.empty_b[sb]));
+#else
+      (void)a_desc, (void)b_desc, (void)idesc;
+#endif
+      tc_commit(smem_u32(&sm.empty[sa]));
     }
     if (ok) tc_commit(smem_u32(&sm.acc_full));
   }
@@ -280,12 +289,10 @@ int trellis_tc_multiply(qtip_matrix w, const uint16_t* x, float* z, int stride, 
   }
   const dim3 grid(w.out / kFtRows, (tokens + n_tile - 1) / n_tile, splits);
   QB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, QTIP_E_GEOMETRY, "too many token tiles or splits");
-  if (ft_stages_a(n_tile) == 4)
-    trellis_tc_kernel<4><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile,
-                                                                   ft_stages_b(n_tile), splits, status);
+  if (ft_stages(n_tile) == 4)
+    trellis_tc_kernel<4><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile, splits, status);
   else
-    trellis_tc_kernel<2><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile,
-                                                                   ft_stages_b(n_tile), splits, status);
+    trellis_tc_kernel<2><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile, splits, status);
   QB_LAUNCHED();
   return QTIP_OK;
 }

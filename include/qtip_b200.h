@@ -133,6 +133,20 @@ int qtip_k_viterbi_finish_words(const uint32_t* bp_d, const uint16_t* final_stat
                                 int nblk, int blk, float* hat_d, float* hatWT_d, long m, int col0,
                                 const uint32_t* lut_h2_d, void* stream);
 
+/* One linear of a Hessian group, end to end on one stream: the per-linear body of quantize_group
+ * (src/quantizer.cpp:236-320). W_d [m][n] f32 (overwritten), L_d [n][n] f32 strictly block-lower (block LDL of the
+ * rotated, damped Hessian), su_d [n] / sv_d [m] sign vectors, lut_h2_d / lut_rms from qtip_encoder_lut.
+ * Steps: Wr = T_m^T diag(SV) W diag(SU) T_n kept transposed in WT_d [n][m]; Wscale = rms(Wr) / (float(lut_rms) *
+ * scale_override), returned in *wscale_out (host) and divided out of WT_d; LDLQ + Viterbi (hatWT_d [n][m], Q_d
+ * [(m/16)(n/16)][128] states); bit packing and kernel layout into trellis_d [(m/16)(n/16)][32]. Synchronises the
+ * stream once, where the reference reads the rms back. The checkpoint tensors are trellis_d, SU as bf16 and
+ * SV * Wscale (src/pipeline.cpp:329-340). Needs m % 32 == 0, n % 128 == 0. */
+size_t qtip_quantize_linear_workspace_bytes(long m, long n);
+int qtip_quantize_linear(float* W_d, const float* L_d, long m, long n, const float* su_d, const float* sv_d,
+                         const uint32_t* lut_h2_d, double lut_rms, double scale_override, float* WT_d, float* hatWT_d,
+                         uint16_t* Q_d, uint16_t* trellis_d, float* wscale_out, void* workspace_d, size_t workspace_bytes,
+                         void* stream);
+
 /* X_d[(tr * (n/16) + tc)][p] = W_d[16 tr + r][16 tc + c], 16 r + c = perm(p): the sequences of every 16x16 tile of a
  * row-major m x n matrix (row stride ld), i.e. what k_ldlq_prep produces block by block when the Hessian is the
  * identity (L = 0, prod = 0; src/viterbi.hip:241-267). */

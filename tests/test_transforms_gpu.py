@@ -202,3 +202,25 @@ def test_quantize_linear_round_trip_through_the_runtime_operator(gpu, oracle):
     err = np.linalg.norm(y.float().cpu().numpy() - y_ref) / np.linalg.norm(y_ref)
     assert err < 2e-2, err  # bf16 LUT, bf16 rotated input and bf16 output against an fp64 dense product
     assert np.linalg.norm(What - W) / np.linalg.norm(W) < 0.5  # 2 bits per weight: the reconstruction is W-like
+
+
+def test_quantize_linear_as_one_call_matches_the_assembled_steps(gpu, oracle):
+    """qtip_quantize_linear against the same steps issued one by one from the host mirror: every output bit for bit."""
+    s = gpu.synth
+    m, n = 96, 256
+    rng = np.random.default_rng(55)
+    W = (0.03 * rng.standard_normal((m, n))).astype(np.float32)
+    H = s.spd_hessian(n, 56)
+    su, sv = s.signs(n, 9), s.signs(m, 10)
+    lut_d, lut_rms = gpu.codec.device_lut(s.seeded_tlut(1))
+    HRr, _ = gpu.codec.rotate_hessian(dev(H.astype(np.float32)), dev(su))
+    Hs = HRr.cpu().numpy().astype(np.float64)
+    L = dev(oracle.block_ldl(0.5 * (Hs + Hs.T)))
+    a = gpu.codec.quantize_linear(dev(W), L, dev(su), dev(sv), lut_d, lut_rms)
+    b = gpu.codec.quantize_linear_fused(dev(W), L, dev(su), dev(sv), lut_d, lut_rms)
+    b["workspace"].check()
+    assert a["wscale"] == b["wscale"]
+    for key in ("WT", "hatWT", "Q", "trellis", "SV"):
+        assert torch.equal(a[key], b[key]), key
+    with pytest.raises(gpu.QtipError):
+        gpu.codec.quantize_linear_fused(dev(W[:80]), L, dev(su), dev(sv[:80]), lut_d, lut_rms)  # m % 32 != 0
