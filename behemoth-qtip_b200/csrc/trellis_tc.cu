@@ -3,36 +3,41 @@
 // weights is ever written: the codes are read once per 256-token tile, which is what keeps this regime on the HBM
 // roofline of the codes instead of that of bf16 weights.
 //
-// One CTA owns 128 output rows (four 32-row block-rows) x one token tile (N = 64, 128 or 256 tokens) x one K-split.
-// Per K step (64 input columns = two 32-column blocks per block-row):
-//   warps 0..15 (decoders), in G groups (4, or 2 with 256-token tiles); group g owns the K steps k = g (mod G) and
-//       stage g of the A ring, so G steps are being decoded at once and a warp meets a barrier only once per whole
-//       32 x 32 block or two. Per block: 8 bytes of codes per lane, the neighbour's words by shuffle, four windows of
-//       four states, sixteen look-ups in the 32-copy table (as the GEMV kernel), and four stmatrix.x4: the four
-//       look-ups of a window are exactly an m16n8k16 A fragment, i.e. four 8 x 8 bf16 matrices, and stmatrix writes them
-//       as 16-byte rows to the addresses the lanes name -- here the K-major, 128-byte-swizzled positions tcgen05
-//       expects (row r, 16-byte chunk c at r * 128 + ((c ^ (r & 7)) << 4)). Eight consecutive rows hit eight different
-//       chunk positions: no bank conflicts. Then fence.proxy.async (the MMA reads through the async proxy) and one
-//       arrive per warp on the stage's barrier.
-//   warp 16, one lane : TMA loads of the activation tile (N tokens x 64 columns, K-major, 128-byte swizzle, zero fill
-//       beyond the last token) into a ring of their own (deeper than the A ring), completion by mbarrier tx bytes.
-//   warp 17, one lane : four tcgen05.mma (M128 x N x K16) per step into N TMEM columns, tcgen05.commit on the "empty"
-//       barriers of the A and the B stage; after the last step a commit on "accumulator full". Warp 17 also allocates
-//       and frees TMEM.
-//   warps 0..3 again  : epilogue, tcgen05.ld of their 32 TMEM lanes, coalesced fp32 stores of z.
+// Work item = 128 output rows (four 32-row block-rows) x one token tile (N = 64, 128 or 256 tokens) x one K-split.
+// The kernel is persistent: one CTA per SM walks its items (item = CTA, CTA + grid, ...) and every role keeps a running
+// K-step index, so the stage ring, the table in shared memory and the TMEM allocation live across items and the
+// pipeline never drains between them. Per K step (64 input columns = two 32-column blocks per block-row):
+//   warps 0..15 (decoders), in G groups (4, or 2 with 128/256-token tiles); group g owns the steps gk = g (mod G) and
+//       stage g of the ring, so G steps are being decoded at once and a warp meets a barrier only once per whole
+//       32 x 32 block or two. Per block: 8 bytes of codes per lane (requested 4 G steps ahead), the neighbour's words
+//       by shuffle, four windows of four states, sixteen look-ups in the 32-copy table (as the GEMV kernel), and four
+//       stmatrix.x4: the four look-ups of a window are exactly an m16n8k16 A fragment, i.e. four 8 x 8 bf16 matrices,
+//       and stmatrix writes them as 16-byte rows to the addresses the lanes name -- here the K-major, 128-byte-swizzled
+//       positions tcgen05 expects (row r, 16-byte chunk c at r * 128 + ((c ^ (r & 7)) << 4)). Eight consecutive rows
+//       hit eight different chunk positions: no bank conflicts. Then fence.proxy.async (the MMA reads through the
+//       async proxy) and one arrive per warp on the stage's "full" barrier.
+//   warp 16, one lane : TMA load of the step's activation tile (N tokens x 64 columns, K-major, 128-byte swizzle, zero
+//       fill beyond the last token) into the same stage; its transaction bytes complete the same "full" barrier.
+//   warp 17, one lane : ONE wait, four tcgen05.mma (M128 x N x K16) and ONE tcgen05.commit (on the stage's "empty"
+//       barrier) per step -- with few tokens an MMA is short, and the waits and commits of this single thread set the
+//       pace, so there is exactly one of each. Item i accumulates in TMEM buffer i & 1; after an item's last step a
+//       commit on "accumulator full". Warp 17 also allocates and frees the 2 N TMEM columns.
+//   warps 18..21      : epilogue of item i (tcgen05.ld of their 32 TMEM lanes, coalesced fp32 stores of z) under the
+//       main loop of item i + 1, then an arrive on "accumulator empty".
 // Every mbarrier wait is bounded (tc_wait): on a time-out the CTA's abort flag and the status word are raised, all
 // roles fall through, TMEM is freed and the kernel returns.
 #include "tc_common.cuh"
 
 namespace qb {
 
-constexpr int kFtRows = 128, kFtK = 64, kFtDecoders = 16, kFtThreads = (kFtDecoders + 2) * 32;
+constexpr int kFtRows = 128, kFtK = 64, kFtDecoders = 16, kFtEpilogueWarps = 4;
+constexpr int kFtThreads = (kFtDecoders + 2 + kFtEpilogueWarps) * 32;
 constexpr uint32_t kFtABytes = kFtRows * kFtK * 2;  // 16 KiB per stage
 constexpr int kFtLutBytes = 1024 * 32 * 4;         // 32 copies of the table
 constexpr int kFtMaxStages = 8;
 
 struct FtSmem {
-  unsigned long long full[kFtMaxStages], empty[kFtMaxStages], acc_full;
+  unsigned long long full[kFtMaxStages], empty[kFtMaxStages], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -56,12 +61,54 @@ __device__ __forceinline__ void stmatrix_x4(uint32_t addr, uint32_t r0, uint32_t
                "r"(r3));
 }
 
-// grid = (out / 128, token tiles, splits). z[(split * tokens + token) * stride + row]. G = decoder groups = A stages.
+// One work item = 128 output rows x one token tile x one K-split.
+struct FtItem {
+  int row0, tok0, split, ks_lo, steps;
+};
+__device__ __forceinline__ FtItem ft_item(int item, int tok_tiles, int splits, int k_total, int n_tile) {
+  FtItem it;
+  it.split = item % splits;
+  const int t = item / splits;
+  it.tok0 = (t % tok_tiles) * n_tile;
+  it.row0 = (t / tok_tiles) * kFtRows;
+  it.ks_lo = int(long(k_total) * it.split / splits);
+  it.steps = int(long(k_total) * (it.split + 1) / splits) - it.ks_lo;  // >= 1: the host keeps splits <= k_total
+  return it;
+}
+// Walks the K steps of this CTA's items (item = first + i * stride) as one long sequence with a running index `gk`:
+// stage and barrier parity of a step depend on gk alone, so the ring keeps turning across item boundaries.
+struct FtWalk {
+  int item, n_items, stride, tok_tiles, splits, k_total, n_tile;
+  int gk, base;  // global step index of the cursor, and of the first step of the current item
+  FtItem cur;
+  __device__ __forceinline__ void start(int first, int n_items_, int stride_, int tok_tiles_, int splits_, int k_total_,
+                                        int n_tile_, int gk0) {
+    item = first, n_items = n_items_, stride = stride_, tok_tiles = tok_tiles_, splits = splits_, k_total = k_total_;
+    n_tile = n_tile_, gk = gk0, base = 0;
+    if (item < n_items) cur = ft_item(item, tok_tiles, splits, k_total, n_tile);
+    settle();
+  }
+  __device__ __forceinline__ void settle() {
+    while (item < n_items && gk >= base + cur.steps) {
+      base += cur.steps;
+      item += stride;
+      if (item < n_items) cur = ft_item(item, tok_tiles, splits, k_total, n_tile);
+    }
+  }
+  __device__ __forceinline__ bool done() const { return item >= n_items; }
+  __device__ __forceinline__ int k() const { return gk - base; }  // step inside the current item
+  __device__ __forceinline__ void advance(int by) {
+    gk += by;
+    settle();
+  }
+};
+
+// Persistent: grid = min(SMs, items); CTA c takes items c, c + grid, ... z[(split * tokens + token) * stride + row].
+// G = decoder groups = stages of the ring.
 template <int G>
 __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w, const __grid_constant__ CUtensorMap map_x,
                                                                    float* __restrict__ z, int stride, int tokens, int n_tile,
-                                                                   int splits,
-                                                                   int* __restrict__ status) {
+                                                                   int splits, int n_items, int* __restrict__ status) {
   const uint32_t raw = smem_u32(ft_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1,024-byte alignment
   unsigned char* smem = ft_smem_raw + (base - raw);
@@ -70,10 +117,7 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
   const uint32_t b_bytes = uint32_t(n_tile) * kFtK * 2;
   FtSmem& sm = *reinterpret_cast<FtSmem*>(smem + kFtLutBytes + size_t(G) * (kFtABytes + b_bytes));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * kFtRows, tok0 = blockIdx.y * n_tile, split = blockIdx.z;
-  const int k_total = w.in / kFtK;
-  const int ks_lo = int(long(k_total) * split / splits), ks_hi = int(long(k_total) * (split + 1) / splits);
-  const int k_steps = ks_hi - ks_lo;
+  const int k_total = w.in / kFtK, tok_tiles = (tokens + n_tile - 1) / n_tile;
   volatile int* abort_flag = &sm.abort_flag;
 
   if (threadIdx.x == 0) {
@@ -81,13 +125,16 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
       tc_mbar_init(smem_u32(&sm.full[s]), kFtDecoders / G + 1);  // the group's warps + the TMA lane (with its bytes)
       tc_mbar_init(smem_u32(&sm.empty[s]), 1);
     }
-    tc_mbar_init(smem_u32(&sm.acc_full), 1);
+    for (int b = 0; b < 2; ++b) {
+      tc_mbar_init(smem_u32(&sm.acc_full[b]), 1);
+      tc_mbar_init(smem_u32(&sm.acc_empty[b]), kFtEpilogueWarps);
+    }
     sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == kFtDecoders + 1) {  // TMEM allocation: whole warp, n_tile columns (a power of two >= 32)
+  if (warp == kFtDecoders + 1) {  // TMEM allocation: whole warp, two accumulators of n_tile columns
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
-                 "r"(uint32_t(n_tile))
+                 "r"(uint32_t(2 * n_tile))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -108,8 +155,8 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
   const uint32_t tmem = sm.tmem_base;
 
   if (warp < kFtDecoders) {
-    // ---- decoders: G groups of 16 / G warps; group g decodes the K steps k = g (mod G) into stage g of the A ring, so
-    // G steps are in the making at any time and a warp meets a barrier once per G / 2 whole 32 x 32 blocks.
+    // ---- decoders: G groups of 16 / G warps; group g decodes the steps gk = g (mod G) into stage g, so G steps are in
+    // the making at any time and a warp meets a barrier once per G / 2 whole 32 x 32 blocks.
     constexpr int kWpg = kFtDecoders / G, kBpw = 8 / kWpg;  // warps per group, blocks per warp and step (G / 2)
     const int grp = warp / kWpg, mem = warp % kWpg;
     const int n2 = w.in / 32;
@@ -117,38 +164,46 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
     // stmatrix row addresses of this lane inside a 16 x 16 tile: matrix q = lane >> 3 (q & 1: rows + 8, q >> 1:
     // columns + 8), row lane & 7
     const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8, lchunk = lane >> 4;
-    const uint2* codes[kBpw];
     int brl[kBpw], kbl[kBpw];
 #pragma unroll
     for (int i = 0; i < kBpw; ++i) {
       const int blk = mem * kBpw + i;  // block of the step: block-row blk >> 1, column block blk & 1
       brl[i] = blk >> 1, kbl[i] = blk & 1;
-      codes[i] = reinterpret_cast<const uint2*>(w.trellis) + (size_t(row0 / 32 + brl[i]) * n2 + kbl[i]) * 32 + lane;
     }
+    const uint2* codes = reinterpret_cast<const uint2*>(w.trellis) + lane;
+    auto fetch = [&](const FtWalk& wk, uint2(&dst)[kBpw]) {
+      // block (block-row, column block) of K step ks: 8-byte unit ((br * n2 + 2 ks + kbl) * 32 + lane)
+      const FtWalk& x = wk;
+      const bool live = !x.done();
+      const int ks = live ? x.cur.ks_lo + x.k() : 0, r0 = live ? x.cur.row0 / 32 : 0;
+#pragma unroll
+      for (int i = 0; i < kBpw; ++i) dst[i] = codes[(size_t(r0 + brl[i]) * n2 + 2 * ks + kbl[i]) * 32];
+    };
     constexpr int kAhead = 4;  // group steps of codes in flight per lane (= 4 G K steps)
     uint2 next[kAhead][kBpw];
-    const int first = ks_lo + grp;
+    FtWalk use, pre;  // the step being decoded, and the step whose codes are being requested (kAhead group steps later)
+    use.start(blockIdx.x, n_items, gridDim.x, tok_tiles, splits, k_total, n_tile, grp);
+    pre = use;
 #pragma unroll
-    for (int q = 0; q < kAhead; ++q)
-#pragma unroll
-      for (int i = 0; i < kBpw; ++i) next[q][i] = codes[i][size_t(min(first + q * G, ks_hi - 1)) * 64];
+    for (int q = 0; q < kAhead; ++q) {
+      fetch(pre, next[q]);
+      pre.advance(G);
+    }
     bool ok = true;
-    for (int k0 = grp; k0 < k_steps && ok; k0 += kAhead * G) {
+    while (!use.done() && ok) {
 #pragma unroll
       for (int q = 0; q < kAhead; ++q) {
-        const int kk = k0 + q * G;  // K step relative to ks_lo
-        if (kk >= k_steps) break;
+        if (use.done()) break;
         uint2 own[kBpw];
 #pragma unroll
-        for (int i = 0; i < kBpw; ++i) {
-          own[i] = next[q][i];
-          next[q][i] = codes[i][size_t(min(ks_lo + kk + kAhead * G, ks_hi - 1)) * 64];
-        }
-        if (kk >= G && !tc_wait(smem_u32(&sm.empty[grp]), uint32_t((kk / G - 1) & 1), abort_flag, status)) {
+        for (int i = 0; i < kBpw; ++i) own[i] = next[q][i];
+        fetch(pre, next[q]);
+        pre.advance(G);
+        const int uses = use.gk / G;  // earlier uses of stage `grp`
+        if (uses >= 1 && !tc_wait(smem_u32(&sm.empty[grp]), uint32_t((uses - 1) & 1), abort_flag, status)) {
           ok = false;
           break;
         }
-#ifndef QB_FT_NODECODE
 #pragma unroll
         for (int i = 0; i < kBpw; ++i) {
           const uint2 peer = make_uint2(__shfl_sync(0xffffffffu, own[i].x, (lane + 1) & 31),
@@ -171,67 +226,70 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
             }
           }
         }
-#else  // timing experiment only: the synchronisation skeleton without the decode work
-        if (own[0].x == 0x12345678u) stmatrix_x4(a_tile, own[0].x, own[0].y, 0, 0);
-        (void)lrow, (void)lchunk, (void)brl, (void)kbl;
-#endif
-#ifndef QB_FT_NOFENCE
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
         __syncwarp();
         if (lane == 0) tc_mbar_arrive(smem_u32(&sm.full[grp]));
+        use.advance(G);
       }
     }
   } else if (warp == kFtDecoders) {
     // ---- TMA producer of the activation tiles
     if (lane == 0) {
-      for (int k = 0; k < k_steps; ++k) {
-        const int s = k % G;
-        if (k >= G && !tc_wait(smem_u32(&sm.empty[s]), uint32_t((k / G - 1) & 1), abort_flag, status)) break;
+      FtWalk wk;
+      wk.start(blockIdx.x, n_items, gridDim.x, tok_tiles, splits, k_total, n_tile, 0);
+      for (; !wk.done(); wk.advance(1)) {
+        const int s = wk.gk % G, uses = wk.gk / G;
+        if (uses >= 1 && !tc_wait(smem_u32(&sm.empty[s]), uint32_t((uses - 1) & 1), abort_flag, status)) break;
         const uint32_t bar = smem_u32(&sm.full[s]);
-#ifndef QB_FT_NOTMA
         tc_mbar_expect_tx(bar, b_bytes);
-        tc_tma_load_2d(b_ring + uint32_t(s) * b_bytes, &map_x, (ks_lo + k) * kFtK, tok0, bar);
-#else
-        tc_mbar_arrive(bar);
-#endif
+        tc_tma_load_2d(b_ring + uint32_t(s) * b_bytes, &map_x, (wk.cur.ks_lo + wk.k()) * kFtK, wk.cur.tok0, bar);
       }
     }
-  } else if (lane == 0) {
-    // ---- MMA issuer
-    const uint32_t idesc = tc_idesc(kFtRows, n_tile);
-    bool ok = true;
-    for (int k = 0; k < k_steps && ok; ++k) {
-      const int sa = k % G, sb = sa;
-      ok = tc_wait(smem_u32(&sm.full[sa]), uint32_t((k / G) & 1), abort_flag, status);
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint64_t a_desc = tc_smem_desc(a_ring + uint32_t(sa) * kFtABytes);
-      const uint64_t b_desc = tc_smem_desc(b_ring + uint32_t(sb) * b_bytes);
-#ifndef QB_FT_NOMMA
+  } else if (warp == kFtDecoders + 1) {
+    // ---- MMA issuer: item i of this CTA accumulates in TMEM buffer i & 1, so the epilogue of one item runs under the
+    // main loop of the next
+    if (lane == 0) {
+      const uint32_t idesc = tc_idesc(kFtRows, n_tile);
+      FtWalk wk;
+      wk.start(blockIdx.x, n_items, gridDim.x, tok_tiles, splits, k_total, n_tile, 0);
+      bool ok = true;
+      for (int i = 0; !wk.done() && ok; ++i) {
+        const int buf = i & 1, steps = wk.cur.steps;
+        if (i >= 2) ok = tc_wait(smem_u32(&sm.acc_empty[buf]), uint32_t(((i >> 1) - 1) & 1), abort_flag, status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int k = 0; k < steps; ++k) {
+          const int s = wk.gk % G;
+          ok = tc_wait(smem_u32(&sm.full[s]), uint32_t((wk.gk / G) & 1), abort_flag, status);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t a_desc = tc_smem_desc(a_ring + uint32_t(s) * kFtABytes);
+          const uint64_t b_desc = tc_smem_desc(b_ring + uint32_t(s) * b_bytes);
 #pragma unroll
-      for (int kk = 0; kk < kFtK / 16; ++kk)
-        tc_mma(tmem, a_desc + uint64_t(2 * kk), b_desc + uint64_t(2 * kk), idesc, k > 0 || kk > 0);
-#else
-      (void)a_desc, (void)b_desc, (void)idesc;
-#endif
-      tc_commit(smem_u32(&sm.empty[sa]));
+          for (int kk = 0; kk < kFtK / 16; ++kk)
+            tc_mma(tmem + uint32_t(buf * n_tile), a_desc + uint64_t(2 * kk), b_desc + uint64_t(2 * kk), idesc,
+                   k > 0 || kk > 0);
+          tc_commit(smem_u32(&sm.empty[s]));
+          wk.advance(1);
+        }
+        if (ok) tc_commit(smem_u32(&sm.acc_full[buf]));
+      }
     }
-    if (ok) tc_commit(smem_u32(&sm.acc_full));
-  }
-
-  if (warp < 4) {
-    // ---- epilogue: warp q reads TMEM lanes 32 q .. 32 q + 31 (rows), columns = tokens of the tile
-    const bool ok = k_steps > 0 && tc_wait(smem_u32(&sm.acc_full), 0, abort_flag, status);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int row = row0 + warp * 32 + lane;
-    float* zs = z + size_t(split) * tokens * stride + row;
+  } else {
+    // ---- epilogue warps: warp e reads TMEM lanes 32 (e % 4) .. + 31 (rows), columns = tokens of the tile
+    const int quarter = warp & 3;
+    int i = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++i) {
+      const FtItem it = ft_item(item, tok_tiles, splits, k_total, n_tile);
+      const int buf = i & 1;
+      if (!tc_wait(smem_u32(&sm.acc_full[buf]), uint32_t((i >> 1) & 1), abort_flag, status)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float* zs = z + size_t(it.split) * tokens * stride + it.row0 + quarter * 32 + lane;
 #pragma unroll 1
-    for (int cc = 0; cc < n_tile; cc += 32) {
-      if (tok0 + cc >= tokens) break;
-      uint32_t v[32];
-      if (ok) {
-        const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16) + uint32_t(cc);
+      for (int cc = 0; cc < n_tile; cc += 32) {
+        if (it.tok0 + cc >= tokens) break;
+        uint32_t v[32];
+        const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(buf * n_tile + cc);
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -243,24 +301,23 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      } else {
-#pragma unroll
-        for (int c = 0; c < 32; ++c) v[c] = 0u;  // an empty K range (more splits than K steps) contributes zeros
-      }
-      if (ok || k_steps == 0) {
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const int tok = tok0 + cc + c;
+          const int tok = it.tok0 + cc + c;
           if (tok < tokens) zs[size_t(tok) * stride] = __uint_as_float(v[c]);
         }
       }
+      // the accumulator has been read: hand the buffer back to the MMA thread
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) tc_mbar_arrive(smem_u32(&sm.acc_empty[buf]));
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == kFtDecoders + 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(n_tile)) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(2 * n_tile)) : "memory");
   }
 }
 
@@ -287,12 +344,21 @@ int trellis_tc_multiply(qtip_matrix w, const uint16_t* x, float* z, int stride, 
     QB_CUDA(cudaGetSymbolAddress(&p, g_ft_status));
     status = static_cast<int*>(p);
   }
-  const dim3 grid(w.out / kFtRows, (tokens + n_tile - 1) / n_tile, splits);
-  QB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, QTIP_E_GEOMETRY, "too many token tiles or splits");
+  const DeviceInfo* info = device_info();
+  if (!info) return QTIP_E_DEVICE;
+  // More K-splits than K steps: the surplus slices of z hold zeros, the kernel runs with one step per split.
+  const int k_total = w.in / kFtK, eff = splits < k_total ? splits : k_total;
+  if (eff < splits)
+    QB_CUDA(cudaMemsetAsync(z + size_t(eff) * tokens * stride, 0, size_t(splits - eff) * tokens * stride * sizeof(float), s));
+  const long items = long(w.out / kFtRows) * ((tokens + n_tile - 1) / n_tile) * eff;
+  QB_REQUIRE(items < (1l << 30), QTIP_E_GEOMETRY, "too many work items (%ld)", items);
+  const int grid = int(items < info->sm_count ? items : info->sm_count);
   if (ft_stages(n_tile) == 4)
-    trellis_tc_kernel<4><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile, splits, status);
+    trellis_tc_kernel<4><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile, eff, int(items),
+                                                                   status);
   else
-    trellis_tc_kernel<2><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile, splits, status);
+    trellis_tc_kernel<2><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile, eff, int(items),
+                                                                   status);
   QB_LAUNCHED();
   return QTIP_OK;
 }
