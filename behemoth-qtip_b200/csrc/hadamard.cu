@@ -329,7 +329,10 @@ __global__ __launch_bounds__(1024, 1) void had_chunk_kernel(HadArgs a) {
 }
 
 constexpr int kMaxRowFloats = 57344;  // 224 KiB of the 227 KiB a CTA may hold
-constexpr int kChunkRowsBelow = 32;   // fewer rows than this: K CTAs per row
+#ifndef QB_HAD_CHUNK_ROWS
+#define QB_HAD_CHUNK_ROWS 32
+#endif
+constexpr int kChunkRowsBelow = QB_HAD_CHUNK_ROWS;  // fewer rows than this: K CTAs per row
 
 template <int K, bool T, Mode M>
 static int configure() {
