@@ -37,6 +37,7 @@ SIGNATURES = {
     "qtip_runtime_lut": [_P, _P, _P],
     "qtip_k_ldlq_prep": [_P, _P, _P, _P, _L, _L, _I, _I, _P, _P],
     "qtip_k_viterbi_fwd": [_P, _P, _I, _I, _P, _P, _P, _P],
+    "qtip_k_viterbi_fwd_simple": [_P, _P, _I, _I, _P, _P, _P, _P],
     "qtip_k_viterbi_overlap": [_P, _P, _I, _P, _P],
     "qtip_k_viterbi_finish": [_P, _P, _I, _I, _P, _I, _I, _P, _L, _I, _P, _P],
     "qtip_k_decode_states": [_P, _I, _P, _P, _P],

@@ -69,6 +69,13 @@ def k_viterbi_fwd(X, overlap, roll, B, A, final_state, lut_h2):
                _p(final_state, torch.int16), _p(lut_h2, torch.int32), _stream())
 
 
+def k_viterbi_fwd_simple(X, overlap, roll, B, A, final_state, lut_h2):
+    """k_viterbi_fwd computed by the plain one-CTA-per-sequence kernel (cross-check implementation)."""
+    init()
+    lib().call("qtip_k_viterbi_fwd_simple", _p(X, torch.float32), _p(overlap, torch.int32), roll, B, _p(A, torch.int16),
+               _p(final_state, torch.int16), _p(lut_h2, torch.int32), _stream())
+
+
 def k_viterbi_overlap(A, final_state, B, overlap):
     init()
     lib().call("qtip_k_viterbi_overlap", _p(A, torch.int16), _p(final_state, torch.int16), B, _p(overlap, torch.int32),

@@ -38,6 +38,7 @@ int viterbi_device_setup(DeviceInfo* info);  // viterbi.cu
 int decode_device_setup(DeviceInfo* info);   // decode.cu
 int gemm_tc_device_setup();                   // gemm_tc.cu
 int trellis_tc_device_setup();                // trellis_tc.cu
+int viterbi_read_status(int* value, cudaStream_t s);  // viterbi.cu: status word of kernel-level cluster launches
 int hadamard_device_setup();                 // hadamard.cu: uploads the order-12/20/28 factors
 
 // Order-K Hadamard factor (Paley construction), K in {12, 20, 28}; row-major +-1. Returns false otherwise.

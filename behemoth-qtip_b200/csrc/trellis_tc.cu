@@ -376,9 +376,12 @@ extern "C" int qtip_multiply_tc(qtip_matrix w, const uint16_t* rotated_d, float*
   return trellis_tc_multiply(w, rotated_d, z_d, stride, splits, tokens, status_d, as_stream(stream));
 }
 extern "C" int qtip_kernel_status(void* stream) {
-  int h = 0;
+  int h = 0, v = 0;
   QB_CUDA(cudaMemcpyFromSymbolAsync(&h, g_ft_status, sizeof h, 0, cudaMemcpyDeviceToHost, as_stream(stream)));
+  int rc = viterbi_read_status(&v, as_stream(stream));
+  if (rc) return rc;
   QB_CUDA(cudaStreamSynchronize(as_stream(stream)));
   QB_REQUIRE(h == 0, QTIP_E_KERNEL, "a bounded pipeline wait of a tensor-core kernel ran out (status %d)", h);
+  QB_REQUIRE(v == 0, QTIP_E_KERNEL, "a bounded wait of the cluster Viterbi kernel ran out (status %d)", v);
   return QTIP_OK;
 }

@@ -278,8 +278,29 @@ __device__ __forceinline__ void wait_full(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-// X [B][256]; overlap [B] or null; bp [B][16][4096] uint32: word (b, i >> 3, j) holds the back-pointer of step i of group
-// j in bits [4 (7 - (i & 7)), +4); blocks below first_blk are not stored. final_state [B].
+// Back-pointers of eight steps (one 32-bit word per thread, oldest step in the top nibble) written in the layout of the
+// reference's k_viterbi_fwd: A[step][j >> 2] uint16, nibble j & 3. The four lanes of a quad own j & 3 = 0..3; lane q
+// collects byte 3 - q (steps 2 q, 2 q + 1) of all four words and squeezes the nibbles of each step into one uint16.
+__device__ __forceinline__ void store_ref_layout(uint16_t* __restrict__ Ab, int blk, int j, uint32_t h, int last_step) {
+  const int q = threadIdx.x & 3;
+  uint32_t w = 0;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const uint32_t other = __shfl_sync(0xffffffffu, h, (threadIdx.x & 28) | r, 32);  // word of the lane with j & 3 == r
+    w |= ((other >> (8 * (3 - q))) & 0xffu) << (8 * r);
+  }
+  uint32_t hi = (w >> 4) & 0x0f0f0f0fu, lo = w & 0x0f0f0f0fu;  // nibbles of step 2 q and of step 2 q + 1, one per byte
+  hi = (hi | (hi >> 4)) & 0x00ff00ffu, hi = (hi | (hi >> 8)) & 0xffffu;
+  lo = (lo | (lo >> 4)) & 0x00ff00ffu, lo = (lo | (lo >> 8)) & 0xffffu;
+  const int s0 = blk * 8 + 2 * q;
+  if (s0 <= last_step) Ab[size_t(s0) * 1024 + (j >> 2)] = uint16_t(hi);
+  if (s0 + 1 <= last_step) Ab[size_t(s0 + 1) * 1024 + (j >> 2)] = uint16_t(lo);
+}
+
+// X [B][256]; overlap [B] or null; final_state [B]. Back-pointers, kRefOut = false: bp [B][16][4096] uint32, word
+// (b, i >> 3, j) holds the back-pointer of step i of group j in bits [4 (7 - (i & 7)), +4); blocks below first_blk are
+// not stored. kRefOut = true: the reference's [B][127][1024] uint16 table (see store_ref_layout).
+template <bool kRefOut>
 __global__ __cluster_dims__(kCl, 1, 1) __launch_bounds__(kClThreads, 1) void vit_fwd_cluster_kernel(
     const float* __restrict__ X, const int* __restrict__ overlap, int roll, int B, uint32_t* __restrict__ bp,
     int first_blk, uint16_t* __restrict__ final_state, const uint32_t* __restrict__ lut_h2, int* __restrict__ status,
@@ -401,8 +422,13 @@ __global__ __cluster_dims__(kCl, 1, 1) __launch_bounds__(kClThreads, 1) void vit
         if (blk >= first_blk) {
 #pragma unroll
           for (int t = 0; t < kTB; ++t)
-            if (t_first + t < B)
-              bp[(size_t(t_first + t) * 16 + blk) * 4096 + j] = (i == 126) ? (hist[t] << 4) : hist[t];
+            if (t_first + t < B) {  // uniform over the CTA: the quad shuffles of the reference layout are safe
+              const uint32_t h = (i == 126) ? (hist[t] << 4) : hist[t];
+              if constexpr (kRefOut)
+                store_ref_layout(reinterpret_cast<uint16_t*>(bp) + size_t(t_first + t) * 127 * 1024, blk, j, h, 126);
+              else
+                bp[(size_t(t_first + t) * 16 + blk) * 4096 + j] = h;
+            }
         }
       }
     }
@@ -496,8 +522,16 @@ __global__ void vit_finish_w_kernel(const uint32_t* __restrict__ bp, const uint1
 
 // ------------------------------------------------------------------------------------------------- host side
 
+__device__ int g_vit_status;  // time-outs of cluster launches made through the kernel-level entry point
+int viterbi_read_status(int* value, cudaStream_t s) {
+  QB_CUDA(cudaMemcpyFromSymbolAsync(value, g_vit_status, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
+  return QTIP_OK;
+}
+
 int viterbi_device_setup(DeviceInfo* info) {
-  QB_CUDA(cudaFuncSetAttribute(vit_fwd_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  QB_CUDA(cudaFuncSetAttribute(vit_fwd_cluster_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               int(sizeof(ClusterSmem))));
+  QB_CUDA(cudaFuncSetAttribute(vit_fwd_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                int(sizeof(ClusterSmem))));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(kCl * 64);
@@ -511,7 +545,7 @@ int viterbi_device_setup(DeviceInfo* info) {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int n = 0;
-  QB_CUDA(cudaOccupancyMaxActiveClusters(&n, vit_fwd_cluster_kernel, &cfg));
+  QB_CUDA(cudaOccupancyMaxActiveClusters(&n, vit_fwd_cluster_kernel<false>, &cfg));
   QB_REQUIRE(n > 0, QTIP_E_DEVICE, "the device cannot co-schedule an %d-CTA cluster of the Viterbi kernel", kCl);
   info->max_clusters = n;
   return QTIP_OK;
@@ -549,13 +583,13 @@ static bool carve_workspace(void* ws, size_t bytes, QuantWorkspace* out) {
   return true;
 }
 
+template <bool kRefOut = false>
 static int launch_cluster_fwd(const DeviceInfo* info, const float* X, const int* overlap, int roll, int B, uint32_t* bp,
                               int first_blk, uint16_t* fs, const uint32_t* lut, int* status, cudaStream_t s) {
   const int batches = (B + kTB - 1) / kTB;
   const int clusters = batches < info->max_clusters ? batches : info->max_clusters;
-  vit_fwd_cluster_kernel<<<dim3(clusters * kCl), dim3(kClThreads), sizeof(ClusterSmem), s>>>(X, overlap, roll, B, bp,
-                                                                                             first_blk, fs, lut, status,
-                                                                                             kTagMask);
+  vit_fwd_cluster_kernel<kRefOut><<<dim3(clusters * kCl), dim3(kClThreads), sizeof(ClusterSmem), s>>>(
+      X, overlap, roll, B, bp, first_blk, fs, lut, status, kTagMask);
   QB_LAUNCHED();
   return QTIP_OK;
 }
@@ -592,6 +626,20 @@ using namespace qb;
 extern "C" int qtip_k_viterbi_fwd(const float* X_d, const int* overlap_d, int roll, int B, uint16_t* A_d,
                                   uint16_t* final_state_d, const uint32_t* lut_h2_d, void* stream) {
   QB_REQUIRE(X_d && A_d && final_state_d && lut_h2_d && B >= 0, QTIP_E_ARG, "qtip_k_viterbi_fwd: bad argument");
+  if (B == 0) return QTIP_OK;
+  // The cluster kernel with the reference's back-pointer layout as its output; its bounded waits report through a word
+  // inside the library (qtip_kernel_status), since this entry point has no status argument.
+  const DeviceInfo* info = device_info();
+  if (!info) return QTIP_E_DEVICE;
+  void* st = nullptr;
+  QB_CUDA(cudaGetSymbolAddress(&st, g_vit_status));
+  return launch_cluster_fwd<true>(info, X_d, overlap_d, roll, B, reinterpret_cast<uint32_t*>(A_d), 0, final_state_d,
+                                  lut_h2_d, static_cast<int*>(st), as_stream(stream));
+}
+// The one-CTA-per-sequence kernel behind the same arguments (kept as a simple second implementation for tests).
+extern "C" int qtip_k_viterbi_fwd_simple(const float* X_d, const int* overlap_d, int roll, int B, uint16_t* A_d,
+                                         uint16_t* final_state_d, const uint32_t* lut_h2_d, void* stream) {
+  QB_REQUIRE(X_d && A_d && final_state_d && lut_h2_d && B >= 0, QTIP_E_ARG, "qtip_k_viterbi_fwd_simple: bad argument");
   if (B == 0) return QTIP_OK;
   vit_fwd_tile_kernel<<<unsigned(B), kTileThreads, 0, as_stream(stream)>>>(X_d, overlap_d, roll, A_d, final_state_d,
                                                                           lut_h2_d, kTagMask);

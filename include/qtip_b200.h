@@ -61,6 +61,10 @@ int qtip_k_ldlq_prep(const float* WT_d, const float* hatWT_d, const float* prod_
  * NULL, roll = 1 reads X rolled by 128. src/viterbi.hip:49-188,275-279 (k_viterbi_fwd). */
 int qtip_k_viterbi_fwd(const float* X_d, const int* overlap_d, int roll, int B, uint16_t* A_d,
                        uint16_t* final_state_d, const uint32_t* lut_h2_d, void* stream);
+/* Same arguments and results, computed by a plain one-CTA-per-sequence kernel (a second, independent implementation kept
+ * for cross-checks; several times slower). */
+int qtip_k_viterbi_fwd_simple(const float* X_d, const int* overlap_d, int roll, int B, uint16_t* A_d,
+                              uint16_t* final_state_d, const uint32_t* lut_h2_d, void* stream);
 /* Pass-1 backtrace: overlap[b] = state(step 64) >> 4. src/viterbi.hip:197-205,280-283 (k_viterbi_overlap). */
 int qtip_k_viterbi_overlap(const uint16_t* A_d, const uint16_t* final_state_d, int B, int* overlap_d, void* stream);
 /* Pass-2 backtrace: states into Q_d[(b0+b)*nblk+blk][128] (may be NULL) and decoded values scattered into
@@ -228,7 +232,8 @@ int qtip_prefill_gemm(const uint16_t* w_dense_d, const uint16_t* x_d, float* z_d
  * decode + library GEMM of runtime/cuda/tensor_model.cpp:210-222. */
 int qtip_multiply_tc(qtip_matrix w, const uint16_t* rotated_d, float* z_d, int stride, int splits, int tokens,
                      int* status_d, void* stream);
-/* Synchronises `stream`; QTIP_E_KERNEL if a tensor-core kernel launched without a status word reported a time-out. */
+/* Synchronises `stream`; QTIP_E_KERNEL if a kernel launched through an entry point without a status argument
+ * (qtip_multiply_batch's tensor-core path, qtip_k_viterbi_fwd) reported a bounded wait that ran out. */
 int qtip_kernel_status(void* stream);
 
 /* FP8 (e4m3) W8A16 projection of the K/V weights kept beside the QTIP linears: y[t][o] = bf16((sum_i fp8(w[o][i]) *

@@ -180,3 +180,24 @@ def test_invariants_at_scale(gpu):
     assert torch.equal(gpu.codec.unpack_trellis(gpu.codec.pack_trellis(st)), st)
     mse = float(((hat - dev(X)) ** 2).mean()) / float((dev(X) ** 2).mean())
     assert 0.05 < mse < 0.2, mse  # a random Gaussian codebook is worse than the trained one (0.07) but well below 1 bit
+
+
+@pytest.mark.parametrize("B", [1, 13, 64])
+def test_kernel_level_forward_two_implementations_agree(gpu, hyb, B):
+    """qtip_k_viterbi_fwd (cluster kernel writing the reference's back-pointer layout) against the plain
+    one-CTA-per-sequence kernel: every back-pointer word and final state, both passes, ragged batch sizes."""
+    tl, _, _ = hyb
+    lut_d, _ = gpu_lut(gpu, tl)
+    X = dev((np.random.default_rng(100 + B).standard_normal((B, 256)) * 1.1).astype(np.float32))
+    c = gpu.codec
+    A, A2 = (torch.zeros((B, 127, 1024), dtype=torch.int16, device="cuda") for _ in range(2))
+    fs, fs2 = (torch.zeros(B, dtype=torch.int16, device="cuda") for _ in range(2))
+    ov = torch.empty(B, dtype=torch.int32, device="cuda")
+    c.k_viterbi_fwd(X, None, 1, B, A, fs, lut_d)
+    c.k_viterbi_fwd_simple(X, None, 1, B, A2, fs2, lut_d)
+    assert torch.equal(A, A2) and torch.equal(fs, fs2)
+    c.k_viterbi_overlap(A, fs, B, ov)
+    c.k_viterbi_fwd(X, ov, 0, B, A, fs, lut_d)
+    c.k_viterbi_fwd_simple(X, ov, 0, B, A2, fs2, lut_d)
+    assert torch.equal(A, A2) and torch.equal(fs, fs2)
+    gpu.linear.kernel_status()
