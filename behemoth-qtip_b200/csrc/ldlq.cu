@@ -9,6 +9,8 @@
 //    128 x 128 output tile per CTA, 8 x 8 per thread, the 128-deep operand panels staged through shared memory.
 //  * qtip_ldlq: the schedule of ldlq_gpu (src/quantizer.cpp:30-89) on one stream, restricted to a slice of W rows.
 #include <cmath>
+#include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -121,10 +123,54 @@ extern "C" int qtip_k_ldlq_prep(const float* WT_d, const float* hatWT_d, const f
   return QTIP_OK;
 }
 
+// Row slices of one call run as independent chains on side streams (rows of W never interact): while one slice is in
+// the last, partly filled round of a Viterbi launch, or in its small prep / backtrace / update kernels, the other
+// slices' launches fill the idle clusters.
+constexpr int kMaxSlices = 4;
+static int ldlq_slices(long ntr) {
+  if (const char* e = std::getenv("QTIP_LDLQ_SLICES")) {
+    const int v = std::atoi(e);
+    if (v >= 1 && v <= kMaxSlices) return ntr >= v ? v : 1;
+  }
+  return ntr >= 256 ? 2 : 1;
+}
+static size_t slice_ws_bytes(long ntr, int slices) {  // Viterbi scratch of all slices together
+  size_t total = 0;
+  for (int i = 0; i < slices; ++i) total += qtip_quantize_workspace_bytes(int(ntr * (i + 1) / slices - ntr * i / slices));
+  return total;
+}
+struct SideStreams {
+  cudaStream_t stream[kMaxSlices - 1] = {};
+  cudaEvent_t fork = nullptr, join[kMaxSlices - 1] = {};
+  bool ready = false;
+};
+static std::mutex g_side_mu;
+static SideStreams g_side[64];
+static int side_streams(SideStreams** out) {
+  int dev = 0;
+  QB_CUDA(cudaGetDevice(&dev));
+  QB_REQUIRE(dev >= 0 && dev < 64, QTIP_E_DEVICE, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_side_mu);
+  SideStreams& sd = g_side[dev];
+  if (!sd.ready) {
+    QB_CUDA(cudaEventCreateWithFlags(&sd.fork, cudaEventDisableTiming));
+    for (int i = 0; i < kMaxSlices - 1; ++i) {
+      QB_CUDA(cudaStreamCreateWithFlags(&sd.stream[i], cudaStreamNonBlocking));
+      QB_CUDA(cudaEventCreateWithFlags(&sd.join[i], cudaEventDisableTiming));
+    }
+    sd.ready = true;
+  }
+  *out = &sd;
+  return QTIP_OK;
+}
+__global__ void merge_status_kernel(int* dst, const int* src) {
+  if (*src) atomicOr(dst, *src);
+}
+
 extern "C" size_t qtip_ldlq_workspace_bytes(long n, long m) {
   if (n <= 0 || m <= 0) return 0;
   const long ntr = m / 16;
-  return qtip_quantize_workspace_bytes(int(ntr)) + align256(size_t(n) * m * 4) + align256(size_t(ntr) * 256 * 4);
+  return slice_ws_bytes(ntr, kMaxSlices) + align256(size_t(n) * m * 4) + align256(size_t(ntr) * 256 * 4);
 }
 
 extern "C" int qtip_ldlq(const float* WT_d, const float* L_d, long n, long m, long j0, long mj, float* hatWT_d,
@@ -136,38 +182,78 @@ extern "C" int qtip_ldlq(const float* WT_d, const float* L_d, long n, long m, lo
   QB_REQUIRE(j0 >= 0 && mj > 0 && j0 % 16 == 0 && mj % 16 == 0 && j0 + mj <= m, QTIP_E_GEOMETRY,
              "LDLQ row slice [%ld, %ld) must be whole 16-row blocks inside m = %ld", j0, j0 + mj, m);
   cudaStream_t s = as_stream(stream);
-  // Workspace: [Viterbi scratch, status word first][prod, full n x m extent, only the slice's columns are touched]
-  // [the slice's sequences]. qtip_workspace_status() therefore works on an LDLQ workspace too.
-  const size_t prod_bytes = align256(size_t(n) * m * 4), x_bytes = align256(size_t(mj / 16) * 256 * 4);
-  const size_t vws_bytes = qtip_quantize_workspace_bytes(int(mj / 16));
+  // Workspace: [Viterbi scratch of every slice, slice 0 (with the status word the caller reads) first][prod, full n x m
+  // extent, only the slice's columns are touched][the sequences]. qtip_workspace_status() therefore works on an LDLQ
+  // workspace too.
+  const int ntr = int(mj / 16), nblk = int(n / 16);
+  const int slices = ldlq_slices(ntr);
+  const size_t prod_bytes = align256(size_t(n) * m * 4), x_bytes = align256(size_t(ntr) * 256 * 4);
+  const size_t vws_bytes = slice_ws_bytes(ntr, slices);
   QB_REQUIRE(workspace_bytes >= vws_bytes + prod_bytes + x_bytes, QTIP_E_WORKSPACE,
              "qtip_ldlq: workspace of %zu bytes is too small (need %zu)", workspace_bytes,
              vws_bytes + prod_bytes + x_bytes);
   unsigned char* p = static_cast<unsigned char*>(workspace_d);
-  void* vws = p;
   float* prod = reinterpret_cast<float*>(p + vws_bytes);
   float* X = reinterpret_cast<float*>(p + vws_bytes + prod_bytes);
-  const int ntr = int(mj / 16), nblk = int(n / 16);
-  QB_CUDA(cudaMemsetAsync(vws, 0, 256, s));  // the status word; it then accumulates over all column steps
+  struct Slice {
+    long j0, mj;
+    int ntr;
+    float* X;
+    void* vws;
+    size_t vws_bytes;
+    cudaStream_t st;
+  } sl[kMaxSlices];
+  SideStreams* side = nullptr;
+  if (slices > 1) {
+    int rc = side_streams(&side);
+    if (rc) return rc;
+  }
+  size_t off = 0;
+  for (int i = 0; i < slices; ++i) {
+    const long t0 = long(ntr) * i / slices, t1 = long(ntr) * (i + 1) / slices;
+    sl[i].j0 = j0 + 16 * t0, sl[i].mj = 16 * (t1 - t0), sl[i].ntr = int(t1 - t0);
+    sl[i].X = X + size_t(t0) * 256;
+    sl[i].vws = p + off, sl[i].vws_bytes = qtip_quantize_workspace_bytes(sl[i].ntr);
+    off += sl[i].vws_bytes;
+    sl[i].st = i == 0 ? s : side->stream[i - 1];
+    QB_CUDA(cudaMemsetAsync(sl[i].vws, 0, 256, s));  // the slice's status word; it accumulates over all column steps
+  }
   zero_cols_kernel<<<148 * 8, 256, 0, s>>>(prod, n, m, j0, mj);
   QB_LAUNCHED();
   zero_cols_kernel<<<148 * 8, 256, 0, s>>>(hatWT_d, n, m, j0, mj);
   QB_LAUNCHED();
+  if (slices > 1) {
+    QB_CUDA(cudaEventRecord(side->fork, s));
+    for (int i = 1; i < slices; ++i) QB_CUDA(cudaStreamWaitEvent(sl[i].st, side->fork, 0));
+  }
   for (long cur = n / 16; cur > 0; cur -= 8) {
     const int bufend = int(16 * cur), c0 = bufend - 128;
     for (int i = 7; i >= 0; --i) {
       const int col0 = c0 + 16 * i;
-      ldlq_prep_kernel<<<blocks_for(mj, 256), 256, 0, s>>>(WT_d, hatWT_d, prod, L_d, n, m, j0, mj, col0, bufend, X);
-      QB_LAUNCHED();
-      int rc = quantize_tiles_impl(X, ntr, int(j0 / 16), lut_h2_d, Q_d, nblk, col0 / 16, nullptr, hatWT_d, m, col0, vws,
-                                   vws_bytes, false, s);
-      if (rc) return rc;
+      for (int q = 0; q < slices; ++q) {  // the same column step of every slice, each on its own stream
+        const Slice& a = sl[q];
+        ldlq_prep_kernel<<<blocks_for(a.mj, 256), 256, 0, a.st>>>(WT_d, hatWT_d, prod, L_d, n, m, a.j0, a.mj, col0, bufend,
+                                                                 a.X);
+        QB_LAUNCHED();
+        int rc = quantize_tiles_impl(a.X, a.ntr, int(a.j0 / 16), lut_h2_d, Q_d, nblk, col0 / 16, nullptr, hatWT_d, m, col0,
+                                     a.vws, a.vws_bytes, false, a.st);
+        if (rc) return rc;
+      }
     }
     if (c0 > 0) {
-      const dim3 grid(blocks_for(mj, kUpTile), blocks_for(c0, kUpTile));
-      ldlq_update_kernel<<<grid, 256, 0, s>>>(WT_d, hatWT_d, L_d, prod, n, m, j0, mj, c0);
-      QB_LAUNCHED();
+      for (int q = 0; q < slices; ++q) {
+        const Slice& a = sl[q];
+        const dim3 grid(blocks_for(a.mj, kUpTile), blocks_for(c0, kUpTile));
+        ldlq_update_kernel<<<grid, 256, 0, a.st>>>(WT_d, hatWT_d, L_d, prod, n, m, a.j0, a.mj, c0);
+        QB_LAUNCHED();
+      }
     }
+  }
+  for (int i = 1; i < slices; ++i) {
+    QB_CUDA(cudaEventRecord(side->join[i - 1], sl[i].st));
+    QB_CUDA(cudaStreamWaitEvent(s, side->join[i - 1], 0));
+    merge_status_kernel<<<1, 1, 0, s>>>(static_cast<int*>(sl[0].vws), static_cast<const int*>(sl[i].vws));
+    QB_LAUNCHED();
   }
   return QTIP_OK;
 }

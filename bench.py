@@ -519,12 +519,23 @@ def ldlq_workload(args):
                           "dtype": "f32", "data": "synthetic",
                           "config": {"workload": "ldlq_viterbi_%dx%d" % (m, n), "column_steps": n // 16,
                                      "sequences_per_step_per_rank": mj // 16, "buffers": n // 128},
+                          "roofline": ldlq_roofline(m, n, ms, world, torch, local),
                           "stages_ms": {"hessian_and_block_ldl_setup_s": t_ldl, "weight_rht_ms": t_rht, "ldlq_ms": ms},
                           "checks": {"trellis_links_and_tail_biting": links, "decode_equals_hatW": decode_ok,
                                      "relative_mse": rel_mse, "wscale": wscale}}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def ldlq_roofline(m, n, ms, world, torch, local):
+    """The whole LDLQ + Viterbi section against the FP32-issue peak of the GPUs used (327,680 lane-ops per weight)."""
+    peaks, peak_src = measured_peaks()
+    sm_count = torch.cuda.get_device_properties(local).multi_processor_count
+    peak = world * sm_count * 128 * peaks.get("sm_max_mhz", 1965.0) * 1e6
+    achieved = m * n * LANE_OPS_PER_WEIGHT / (ms * 1e-3)
+    return {"bound": "fp32_issue", "achieved": achieved / 1e12, "peak": peak / 1e12, "unit": "Tlane-op/s",
+            "frac": achieved / peak, "peak_source": "%d GPU(s) x %d SMs x 128 lanes x sm_max_mhz (%s)" % (world, sm_count, peak_src)}
 
 
 def layer_workload(args):

@@ -224,3 +224,22 @@ def test_quantize_linear_as_one_call_matches_the_assembled_steps(gpu, oracle):
         assert torch.equal(a[key], b[key]), key
     with pytest.raises(gpu.QtipError):
         gpu.codec.quantize_linear_fused(dev(W[:80]), L, dev(su), dev(sv[:80]), lut_d, lut_rms)  # m % 32 != 0
+
+
+@pytest.mark.parametrize("slices", [2, 3, 4])
+def test_ldlq_row_slices_on_side_streams_give_the_same_codes(gpu, oracle, hyb, slices, monkeypatch):
+    """The rows of one call run as 2..4 independent chains on side streams (QTIP_LDLQ_SLICES forces it for this small
+    matrix): states and hatW stay bit-identical to the fp32 restatement of the schedule, and the status word is clean."""
+    tl, lut, _ = hyb
+    m, n = 112, 256  # 7 tile rows: uneven slices
+    Wr, H, L = ldlq_problem(oracle, m, n, 23)
+    WT = np.ascontiguousarray(Wr.T)
+    lut_d, _ = gpu.codec.device_lut(tl)
+    monkeypatch.setenv("QTIP_LDLQ_SLICES", str(slices))
+    hat_d = torch.empty((n, m), dtype=torch.float32, device="cuda")
+    Q_d = torch.zeros(((m // 16) * (n // 16), 128), dtype=torch.int16, device="cuda")
+    ws = gpu.codec.ldlq_gpu(dev(WT), dev(L), n, m, hat_d, Q_d, lut_d)
+    ws.check()
+    ohat, oQ = oracle.ldlq_f32(WT, L, lut)
+    assert np.array_equal(u16(Q_d), oQ)
+    assert np.array_equal(hat_d.cpu().numpy(), ohat)
