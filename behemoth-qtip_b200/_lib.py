@@ -63,6 +63,7 @@ SIGNATURES = {
     "qtip_ldlq": [_P, _P, _L, _L, _L, _L, _P, _P, _P, _P, _Z, _P],
     "qtip_quantize_linear": [_P, _P, _L, _L, _P, _P, _P, C.c_double, C.c_double, _P, _P, _P, _P, C.POINTER(C.c_float), _P,
                              _Z, _P],
+    "qtip_rotate_hessian": [_P, _L, _P, C.c_double, _P, C.POINTER(C.c_double), _P, _P],
     "qtip_pack_trellis": [_P, _L, _P, _P],
     "qtip_unpack_trellis": [_P, _L, _P, _P],
     "qtip_swizzle_for_kernel": [_P, _I, _I, _P, _P],

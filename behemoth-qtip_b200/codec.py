@@ -361,3 +361,15 @@ def quantize_linear_fused(W, L, su, sv, lut_h2, lut_rms, workspace=None, scale_o
                C.byref(wscale), workspace.ptr, workspace.nbytes, _stream())
     return {"trellis": trellis, "SU": su.to(torch.bfloat16), "SV": sv * wscale.value, "wscale": wscale.value, "WT": WT,
             "hatWT": hatWT, "Q": Q, "workspace": workspace}
+
+
+def rotate_hessian_fused(H, su, sigma_reg=1e-2):
+    """rotate_hessian as ONE C-ABI call (qtip_rotate_hessian): same result, bit for bit."""
+    init()
+    n = H.shape[0]
+    HR = torch.empty_like(H)
+    scratch = torch.zeros(1, dtype=torch.float64, device=H.device)
+    creg = C.c_double()
+    lib().call("qtip_rotate_hessian", _p(H, torch.float32), n, _p(su, torch.float32), float(sigma_reg),
+               _p(HR, torch.float32), C.byref(creg), _p(scratch, torch.float64), _stream())
+    return HR, creg.value

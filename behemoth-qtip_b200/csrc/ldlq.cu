@@ -17,8 +17,8 @@
 namespace qb {
 
 int quantize_tiles_impl(const float* X, int B, int b0, const uint32_t* lut, uint16_t* Q, int nblk, int blk, float* hat,
-                        float* hatWT, long m, int col0, void* ws, size_t ws_bytes, bool reset_status,
-                        cudaStream_t s);  // viterbi.cu
+                        float* hatWT, long m, int col0, void* ws, size_t ws_bytes, bool reset_status, cudaStream_t s,
+                        bool two_lanes);  // viterbi.cu
 
 // Rows j in [j0, j0 + mj) of W; X is indexed from the slice start: X[(j - j0) >> 4][256].
 __global__ __launch_bounds__(256) void ldlq_prep_kernel(const float* __restrict__ WT, const float* __restrict__ hatWT,
@@ -236,7 +236,7 @@ extern "C" int qtip_ldlq(const float* WT_d, const float* L_d, long n, long m, lo
                                                                  a.X);
         QB_LAUNCHED();
         int rc = quantize_tiles_impl(a.X, a.ntr, int(a.j0 / 16), lut_h2_d, Q_d, nblk, col0 / 16, nullptr, hatWT_d, m, col0,
-                                     a.vws, a.vws_bytes, false, a.st);
+                                     a.vws, a.vws_bytes, false, a.st, false);
         if (rc) return rc;
       }
     }
@@ -306,4 +306,25 @@ extern "C" int qtip_quantize_linear(float* W_d, const float* L_d, long m, long n
   const long tiles = (m / 16) * (n / 16);
   if ((rc = qtip_pack_trellis(Q_d, tiles, packed, stream))) return rc;
   return qtip_swizzle_for_kernel(packed, int(m), int(n), trellis_d, stream);
+}
+
+// Hessian side of a group (src/quantizer.cpp:124-152): damping by sigma_reg * mean(diag), then the rotation
+// HR = T_n^T diag(SU) H diag(SU) T_n with the same row transform applied to both sides through a transpose.
+extern "C" int qtip_rotate_hessian(float* H_d, long n, const float* su_d, double sigma_reg, float* HR_d, double* creg_out,
+                                   double* scratch_d, void* stream) {
+  QB_REQUIRE(H_d && su_d && HR_d && creg_out && scratch_d && n > 0, QTIP_E_ARG, "qtip_rotate_hessian: bad argument");
+  cudaStream_t s = as_stream(stream);
+  int rc;
+  QB_CUDA(cudaMemsetAsync(scratch_d, 0, sizeof(double), s));
+  if ((rc = qtip_k_diag_sum(H_d, n, scratch_d, stream))) return rc;
+  double tr = 0;
+  QB_CUDA(cudaMemcpyAsync(&tr, scratch_d, sizeof tr, cudaMemcpyDeviceToHost, s));
+  QB_CUDA(cudaStreamSynchronize(s));  // the reference reads the trace back at the same point
+  const double creg = sigma_reg * tr / double(n);
+  *creg_out = creg;
+  if ((rc = qtip_k_add_diag(H_d, n, float(creg), stream))) return rc;
+  if ((rc = qtip_k_scale_rows_cols(H_d, n, n, n, su_d, su_d, stream))) return rc;
+  if ((rc = qtip_k_hadamard_rows(H_d, n, int(n), n, 1, stream))) return rc;
+  if ((rc = qtip_k_transpose(H_d, n, n, n, HR_d, n, stream))) return rc;
+  return qtip_k_hadamard_rows(HR_d, n, int(n), n, 1, stream);
 }

@@ -594,27 +594,73 @@ static int launch_cluster_fwd(const DeviceInfo* info, const float* X, const int*
   return QTIP_OK;
 }
 
-// Shared body of the two fused entry points.
+// One side stream and two events per device for the two-lane schedule below (created on first use, never destroyed).
+struct LaneStreams {
+  cudaStream_t side = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  bool ready = false;
+};
+static std::mutex g_lane_mu;
+static LaneStreams g_lane[64];
+static int lane_streams(LaneStreams** out) {
+  int dev = 0;
+  QB_CUDA(cudaGetDevice(&dev));
+  QB_REQUIRE(dev >= 0 && dev < 64, QTIP_E_DEVICE, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_lane_mu);
+  LaneStreams& l = g_lane[dev];
+  if (!l.ready) {
+    QB_CUDA(cudaStreamCreateWithFlags(&l.side, cudaStreamNonBlocking));
+    QB_CUDA(cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming));
+    QB_CUDA(cudaEventCreateWithFlags(&l.join, cudaEventDisableTiming));
+    l.ready = true;
+  }
+  *out = &l;
+  return QTIP_OK;
+}
+
+// Shared body of the fused entry points. The sequences are processed in chunks that fit the workspace: forward (rolled),
+// overlap, forward (constrained), finish. two_lanes: the workspace is halved and consecutive chunks alternate between
+// the caller's stream and a side stream, so that one chunk's backtrace kernels (one thread per sequence) and the partly
+// filled last round of its forward launches run under the other chunk's forward pass.
 int quantize_tiles_impl(const float* X, int B, int b0, const uint32_t* lut, uint16_t* Q, int nblk, int blk, float* hat,
-                        float* hatWT, long m, int col0, void* ws, size_t ws_bytes, bool reset_status, cudaStream_t s) {
+                        float* hatWT, long m, int col0, void* ws, size_t ws_bytes, bool reset_status, cudaStream_t s,
+                        bool two_lanes) {
   const DeviceInfo* info = device_info();
   if (!info) return QTIP_E_DEVICE;
   QuantWorkspace w;
   QB_REQUIRE(carve_workspace(ws, ws_bytes, &w), QTIP_E_WORKSPACE,
              "workspace of %zu bytes is too small (need at least %zu)", ws_bytes, ws_bytes_for(kTB));
   if (reset_status) QB_CUDA(cudaMemsetAsync(w.status, 0, kWsHeader, s));
-  for (int c0 = 0; c0 < B; c0 += w.cap) {
-    const int nb = B - c0 < w.cap ? B - c0 : w.cap;
+  const int half = w.cap / 2 / kTB * kTB;
+  two_lanes = two_lanes && half >= 16 * kTB && B > half;  // worth it only with several chunks of a useful size
+  LaneStreams* ls = nullptr;
+  if (two_lanes) {
+    int rc = lane_streams(&ls);
+    if (rc) return rc;
+    QB_CUDA(cudaEventRecord(ls->fork, s));
+    QB_CUDA(cudaStreamWaitEvent(ls->side, ls->fork, 0));
+  }
+  const int cap = two_lanes ? half : w.cap;
+  int lane = 0;
+  for (int c0 = 0; c0 < B; c0 += cap, lane ^= 1) {
+    const int nb = B - c0 < cap ? B - c0 : cap;
     const float* xc = X + size_t(c0) * 256;
-    int rc = launch_cluster_fwd(info, xc, nullptr, 1, nb, w.bp, 8, w.fs, lut, w.status, s);
+    const int o = (two_lanes && lane) ? half : 0;  // this lane's part of the scratch arrays
+    cudaStream_t st = (two_lanes && lane) ? ls->side : s;
+    uint32_t* bp = w.bp + size_t(o) * (kBpBytes / 4);
+    int rc = launch_cluster_fwd(info, xc, nullptr, 1, nb, bp, 8, w.fs + o, lut, w.status, st);
     if (rc) return rc;
-    vit_overlap_w_kernel<<<blocks_for(nb, 64), 64, 0, s>>>(w.bp, w.fs, nb, w.ov);
+    vit_overlap_w_kernel<<<blocks_for(nb, 64), 64, 0, st>>>(bp, w.fs + o, nb, w.ov + o);
     QB_LAUNCHED();
-    rc = launch_cluster_fwd(info, xc, w.ov, 0, nb, w.bp, 0, w.fs, lut, w.status, s);
+    rc = launch_cluster_fwd(info, xc, w.ov + o, 0, nb, bp, 0, w.fs + o, lut, w.status, st);
     if (rc) return rc;
-    vit_finish_w_kernel<<<blocks_for(nb, 64), 64, 0, s>>>(w.bp, w.fs, nb, b0 + c0, Q, nblk, blk,
-                                                          hat ? hat + size_t(c0) * 256 : nullptr, hatWT, m, col0, lut);
+    vit_finish_w_kernel<<<blocks_for(nb, 64), 64, 0, st>>>(bp, w.fs + o, nb, b0 + c0, Q, nblk, blk,
+                                                           hat ? hat + size_t(c0) * 256 : nullptr, hatWT, m, col0, lut);
     QB_LAUNCHED();
+  }
+  if (two_lanes) {
+    QB_CUDA(cudaEventRecord(ls->join, ls->side));
+    QB_CUDA(cudaStreamWaitEvent(s, ls->join, 0));
   }
   return QTIP_OK;
 }
@@ -713,7 +759,7 @@ extern "C" int qtip_quantize_tiles(const float* X_d, int B, const uint32_t* lut_
   if (B == 0) return QTIP_OK;
   QB_REQUIRE(X_d && lut_h2_d && B > 0, QTIP_E_ARG, "qtip_quantize_tiles: bad argument");
   return quantize_tiles_impl(X_d, B, 0, lut_h2_d, states_d, 1, 0, hat_d, nullptr, 0, 0, workspace_d, workspace_bytes,
-                             true, as_stream(stream));
+                             true, as_stream(stream), true);
 }
 extern "C" int qtip_quantize_tiles_scatter(const float* X_d, int B, int b0, const uint32_t* lut_h2_d, uint16_t* Q_d,
                                            int nblk, int blk, float* hatWT_d, long m, int col0, void* workspace_d,
@@ -724,7 +770,7 @@ extern "C" int qtip_quantize_tiles_scatter(const float* X_d, int B, int b0, cons
              "qtip_quantize_tiles_scatter: m = %ld does not cover %d row blocks", m, b0 + B);
   if (B == 0) return QTIP_OK;
   return quantize_tiles_impl(X_d, B, b0, lut_h2_d, Q_d, nblk, blk, nullptr, hatWT_d, m, col0, workspace_d,
-                             workspace_bytes, true, as_stream(stream));
+                             workspace_bytes, true, as_stream(stream), true);
 }
 // ---- allocation-free variant of qtip_quantize_tiles
 // Some hosts of this library may not allocate device memory at all: a serving process whose memory pool is sized once at
@@ -762,7 +808,7 @@ extern "C" int qtip_quantize_tiles_noalloc(const float* X_d, int B, const uint32
   // The array keeps whatever the previous call left: the status word is cleared by the shared body (reset_status),
   // every other field is written before it is read.
   return quantize_tiles_impl(X_d, B, 0, lut_h2_d, states_d, 1, 0, hat_d, nullptr, 0, 0, scratch, kNoAllocBytes, true,
-                             as_stream(stream));
+                             as_stream(stream), false);  // one lane: this entry point creates no streams or events
 }
 
 extern "C" int qtip_workspace_status(const void* workspace_d, void* stream) {

@@ -265,8 +265,8 @@ def main():
     gen.manual_seed(2 + 1000003 * b)
     W = torch.randn((e - b) * 16, N_COLS, generator=gen, device="cuda", dtype=torch.float32)
     X = codec.tiles_from_matrix(W)
-    chunk = 4608
-    ws = codec.quantize_workspace(chunk)
+    chunk = 4608  # sequences per forward launch; the workspace holds two chunks, which alternate between two streams
+    ws = codec.quantize_workspace(2 * chunk)
     states = torch.empty((tiles_local, 128), dtype=torch.int16, device="cuda")
     torch.cuda.synchronize()
 
@@ -379,7 +379,8 @@ def main():
                        "l2": ("inputs (%.0f MB per rank) exceed the 126 MB L2" % (tiles_local * 1024 / 1e6)) if flush is None
                        else ("inputs are %.0f MB per rank: a 256 MB buffer is overwritten between steps to flush the L2"
                              % (tiles_local * 1024 / 1e6)),
-                       "sharding": "contiguous tile rows per rank, no collective", "chunk_tiles": chunk},
+                       "sharding": "contiguous tile rows per rank, no collective", "chunk_tiles": chunk,
+                       "chunks_in_flight": 2 if tiles_local > chunk else 1},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "fp32_issue", "kernel": "vit_fwd_cluster_kernel", "achieved": achieved / 1e12,
                          "peak": peak_ops / 1e12, "unit": "Tlane-op/s", "frac": achieved / peak_ops,

@@ -94,7 +94,11 @@ int qtip_k_diff_split_bf16(const float* A_d, const float* B_d, long rows, long c
 /* ------------------------------------------------------------------------------------------------------------
  * Encode side: fused interface (what a caller of ldlq_gpu / quantize_group switches to).
  */
-/* Bytes of device workspace qtip_quantize_tiles needs for up to max_tiles sequences per call. */
+/* Bytes of device workspace qtip_quantize_tiles needs for up to max_tiles sequences per call. A batch larger than
+ * half the workspace's capacity is processed in chunks that alternate between `stream` and a side stream owned by the
+ * library (created on first use per device; joined back into `stream` before the call returns to the host), so that
+ * one chunk's backtraces run under the other's forward pass. qtip_ldlq uses side streams the same way for row slices.
+ * Consequence: on one device, calls of these entry points from different host threads must not overlap in time. */
 size_t qtip_quantize_workspace_bytes(int max_tiles);
 /* Two-pass tail-biting quantisation of B sequences: forward(roll) -> overlap -> forward(overlap) -> backtrace, the
  * call sequence of src/quantizer.cpp:59-62 in one entry point. X_d [B][256] f32 -> states_d [B][128] u16 (may be
@@ -150,6 +154,13 @@ int qtip_quantize_linear(float* W_d, const float* L_d, long m, long n, const flo
                          const uint32_t* lut_h2_d, double lut_rms, double scale_override, float* WT_d, float* hatWT_d,
                          uint16_t* Q_d, uint16_t* trellis_d, float* wscale_out, void* workspace_d, size_t workspace_bytes,
                          void* stream);
+
+/* Hessian side of a group as one call (src/quantizer.cpp:124-152): H_d [n][n] f32 is damped in place by
+ * creg = sigma_reg * mean(diag(H)) (returned through creg_out, host) and rotated, HR_d = T_n^T diag(SU) (H + creg I)
+ * diag(SU) T_n. scratch_d: one double on the device. Synchronises the stream once (the trace is read back). The block LDL
+ * of HR_d is the caller's (the reference computes it on the CPU in fp64, src/qtip_core.cpp:444-487). */
+int qtip_rotate_hessian(float* H_d, long n, const float* su_d, double sigma_reg, float* HR_d, double* creg_out,
+                        double* scratch_d, void* stream);
 
 /* X_d[(tr * (n/16) + tc)][p] = W_d[16 tr + r][16 tc + c], 16 r + c = perm(p): the sequences of every 16x16 tile of a
  * row-major m x n matrix (row stride ld), i.e. what k_ldlq_prep produces block by block when the Hessian is the

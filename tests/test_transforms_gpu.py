@@ -243,3 +243,13 @@ def test_ldlq_row_slices_on_side_streams_give_the_same_codes(gpu, oracle, hyb, s
     ohat, oQ = oracle.ldlq_f32(WT, L, lut)
     assert np.array_equal(u16(Q_d), oQ)
     assert np.array_equal(hat_d.cpu().numpy(), ohat)
+
+
+def test_rotate_hessian_as_one_call(gpu):
+    s = gpu.synth
+    n = 384
+    H = s.spd_hessian(n, 77).astype(np.float32)
+    su = s.signs(n, 3)
+    a, ca = gpu.codec.rotate_hessian(dev(H), dev(su))
+    b, cb = gpu.codec.rotate_hessian_fused(dev(H), dev(su))
+    assert ca == cb and torch.equal(a, b)

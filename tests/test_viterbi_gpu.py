@@ -201,3 +201,20 @@ def test_kernel_level_forward_two_implementations_agree(gpu, hyb, B):
     c.k_viterbi_fwd_simple(X, ov, 0, B, A2, fs2, lut_d)
     assert torch.equal(A, A2) and torch.equal(fs, fs2)
     gpu.linear.kernel_status()
+
+
+def test_two_chunks_in_flight_give_the_same_codes(gpu, hyb):
+    """A workspace smaller than the batch makes the fused call alternate chunks between its stream and a side stream;
+    the result must equal the single-chunk run bit for bit, and the status word must stay clean."""
+    tl, _, _ = hyb
+    lut_d, _ = gpu_lut(gpu, tl)
+    B = 600
+    X = dev((np.random.default_rng(9).standard_normal((B, 256)) * 0.8).astype(np.float32))
+    c = gpu.codec
+    big = c.quantize_workspace(2 * B)      # B <= half of the capacity: one chunk, one stream
+    small = c.quantize_workspace(256)      # chunks of 128 sequences on two streams
+    s1, h1 = c.quantize_tiles(X, lut_d, workspace=big)
+    s2, h2 = c.quantize_tiles(X, lut_d, workspace=small)
+    big.check()
+    small.check()
+    assert torch.equal(s1, s2) and torch.equal(h1, h2)
