@@ -236,6 +236,8 @@ def main():
         return reference_arm(args)
     if args.workload == "ldlq":
         return ldlq_workload(args)
+    if args.workload == "layer" and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return layer_workload_tp(args)
     if args.workload == "layer":
         return layer_workload(args)
 
@@ -527,6 +529,119 @@ def ldlq_workload(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def layer_workload_tp(args):
+    """The layer workload on N GPUs: every linear sharded by output rows (rotated-row tensor parallelism, contiguous
+    32-row block-rows per rank), input transform on every rank, products of the shard, gather, output transform on every
+    rank. <= 16 tokens: products pushed into every rank's gathered buffer by the product kernel (no collective call);
+    64 / 256 tokens: fused decode + tcgen05 product of the shard, K-split partials summed, NCCL all-gather; 2048 tokens:
+    dense decode + tcgen05 GEMM of the shard, NCCL all-gather. K/V (FP8): rows sharded, NCCL all-gather of the outputs.
+    Time per layer = max over ranks, CUDA events (graph replay up to 256 tokens)."""
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    linear, synth, tp = pkg.linear, pkg.synth, pkg.tp
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg.codec.init()
+    peaks, peak_src = measured_peaks()
+    hidden, inter, kv = 12288, 28672, 1024
+    shapes = {"q": (hidden, hidden), "o": (hidden, hidden), "gate": (hidden, inter), "up": (hidden, inter),
+              "down": (inter, hidden)}
+    lut = linear.runtime_lut(synth.seeded_tlut(1))
+    g = torch.Generator(device="cuda")
+    full, shard, row0 = {}, {}, {}
+    for i, (name, (n_in, n_out)) in enumerate(shapes.items()):
+        r0, rows = pkg.sharding.block_row_range(n_out, rank, world)
+        g.manual_seed(9 + i + 100 * rank)
+        tr = torch.randint(-32768, 32768, ((rows // 16) * (n_in // 16) * 32,), generator=g, device="cuda", dtype=torch.int16)
+        su = torch.from_numpy(synth.signs(n_in, 7)).cuda()
+        sv = torch.from_numpy(synth.signs(n_out, 8)).cuda()
+        full[name] = linear.Matrix(None, su, sv, None, n_in, n_out)
+        shard[name] = linear.Matrix(tr, su, sv[r0:r0 + rows].contiguous(), lut, n_in, rows)
+        row0[name] = r0
+    kv_rows = kv // world
+    g.manual_seed(11 + rank)
+    w8 = [torch.randint(0, 255, (kv_rows, hidden), generator=g, device="cuda", dtype=torch.uint8) for _ in range(2)]
+    for w in w8:
+        w[(w & 127) == 127] = 0
+    s8 = ((1 + torch.arange(kv_rows, device="cuda") % 7) / 4096.0).float()
+    code_bytes = sum(a * b // 4 for a, b in shapes.values()) + 2 * kv * hidden
+    weights = sum(a * b for a, b in shapes.values()) + 2 * kv * hidden
+    dense = torch.empty((inter // world) * hidden, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ex = {n_out: tp.Exchange.from_process_group(n_out, max_tokens=16, max_splits=4) for n_out in (hidden, inter)}
+    out = {}
+    for T in (1, 16, 64, 256, 2048):
+        g.manual_seed(10)
+        xs = {n: torch.randn(T, n, generator=g, device="cuda").to(torch.bfloat16) for n in (hidden, inter)}
+        rot = {n: torch.empty(T, n, dtype=torch.bfloat16, device="cuda") for n in (hidden, inter)}
+        ys = {n: torch.empty(T, n, dtype=torch.bfloat16, device="cuda") for n in (hidden, inter)}
+        ykv_l = torch.empty(T, kv_rows, dtype=torch.bfloat16, device="cuda")
+        ykv = torch.empty(world, T, kv_rows, dtype=torch.bfloat16, device="cuda")
+        rows_max = inter // world
+        z_l = torch.empty(4 * T * rows_max, dtype=torch.float32, device="cuda")
+        z_g = torch.empty(world * T * rows_max, dtype=torch.float32, device="cuda")
+        scratch = torch.empty(1, dtype=torch.float32, device="cuda")
+        if 16 < T <= 512:
+            splits = {name: max(1, min(4, -(-2 * 148 // (shard[name].n_out // 128)))) for name in shapes}
+        else:
+            splits = {name: (2 if T <= 16 else 1) for name in shapes}
+
+        def layer():
+            for name, (n_in, n_out) in shapes.items():
+                w, ws, sp = full[name], shard[name], splits[name]
+                rows = ws.n_out
+                if T <= 16:
+                    tp.forward_tp(ex[n_out], w, ws, row0[name], xs[n_in], ys[n_out], scratch, rot[n_in],
+                                  name in ("gate", "up"), sp, T)
+                    continue
+                linear.qtip_prepare(ws, xs[n_in], scratch, rot[n_in], T)
+                zl = z_l[:sp * T * rows]
+                if T > 512:
+                    linear.qtip_multiply_prefill(ws, rot[n_in], zl, rows, T, dense[:rows * n_in].view(rows, n_in), status)
+                else:
+                    linear.qtip_multiply_batch(ws, rot[n_in], zl, rows, sp, T)
+                    linear.reduce_products(zl, T * rows, sp)
+                zg = z_g[:world * T * rows]
+                dist.all_gather_into_tensor(zg, zl[:T * rows])
+                linear.qtip_finish(w, zg, ys[n_out], scratch, name in ("gate", "up"), 1, T, world)
+            for w in w8:
+                if T >= 128:
+                    linear.fp8_forward_prefill(w, s8, xs[hidden], ykv_l, hidden, kv_rows, T, dense[:kv_rows * hidden], z_l)
+                else:
+                    linear.fp8_forward(w, s8, xs[hidden], ykv_l, hidden, kv_rows, T)
+                dist.all_gather_into_tensor(ykv.view(-1), ykv_l.view(-1))
+
+        dist.barrier()
+        us = _graph_us(layer, 2, torch) if T <= 512 else _time_us(layer, 3, torch)
+        t = torch.tensor([us], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t)
+        flops = 2.0 * T * weights
+        out["T%d" % T] = {"layer_us": us, "code_gbs": code_bytes / us / 1e3, "tflops": flops / us / 1e6,
+                          "frac_of_hbm_peak": code_bytes / us / 1e3 / (world * peaks["hbm_gbs"]),
+                          "frac_of_bf16_peak": flops / us / 1e6 / (world * peaks["bf16_tflops"])}
+        del xs, rot, ys, z_l, z_g
+    for e in ex.values():
+        e.check()
+    assert int(status) == 0
+    linear.kernel_status()
+    dist.barrier()
+    for e in ex.values():
+        e.close()
+    if rank == 0:
+        print(json.dumps({"metric": "qtip_layer_products", "unit": "us per layer", "n_gpus": world, "data": "synthetic",
+                          "config": {"workload": "mistral_large_layer_products", "hidden": hidden, "intermediate": inter,
+                                     "code_bytes": code_bytes, "weights": weights, "peaks": peak_src,
+                                     "parallelism": "rotated-row tensor parallel x%d" % world}, "tokens": out}))
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 def ldlq_roofline(m, n, ms, world, torch, local):
