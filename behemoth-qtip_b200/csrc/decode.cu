@@ -27,7 +27,10 @@ int hadamard_finish_b16(const uint16_t* z, const float* sv, uint16_t* y, int n, 
 int trellis_tc_multiply(qtip_matrix w, const uint16_t* x, float* z, int stride, int splits, int tokens, int* status,
                         cudaStream_t s);  // trellis_tc.cu
 
-constexpr int kGemmThreads = 1024;
+#ifndef QB_GEMV_THREADS
+#define QB_GEMV_THREADS 1024
+#endif
+constexpr int kGemmThreads = QB_GEMV_THREADS;  // 1024 (64 registers per thread) or 512 (128)
 constexpr int kWarpsPerItem = 8;
 constexpr int kItemsPerCta = kGemmThreads / 32 / kWarpsPerItem;  // 4
 constexpr int kLutBytes = 1024 * 32 * 4;                         // 128 KiB, 32 copies
@@ -262,10 +265,14 @@ __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matr
   {
     // 32 copies of the table: each thread reads ONE entry from global memory, a warp then spreads its 32 entries with
     // shuffles so that every store instruction writes 32 consecutive words (no bank conflicts, one load latency).
-    const uint32_t mine = w.lut[tid];
     const int lane = tid & 31;
 #pragma unroll
-    for (int e = 0; e < 32; ++e) lut_s[((warp << 5) + e) * 32 + lane] = __shfl_sync(0xffffffffu, mine, e);
+    for (int h = 0; h < 1024 / kGemmThreads; ++h) {
+      const int e0 = (h * (kGemmThreads / 32) + warp) << 5;
+      const uint32_t mine = w.lut[e0 + lane];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) lut_s[(e0 + e) * 32 + lane] = __shfl_sync(0xffffffffu, mine, e);
+    }
   }
   const uint32_t* xw = reinterpret_cast<const uint32_t*>(x) + size_t(t0) * (w.in / 2);
   if constexpr (XS) {
