@@ -76,6 +76,7 @@ SIGNATURES = {
     "qtip_multiply_batch": [QtipMatrix, _P, _P, _I, _I, _I, _P, _I],
     "qtip_decode_matrix": [QtipMatrix, _P, _P],
     "qtip_prefill_gemm": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "qtip_prefill_gemm_splitk": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "qtip_multiply_tc": [QtipMatrix, _P, _P, _I, _I, _I, _P, _P],
     "qtip_kernel_status": [_P],
     "qtip_decode_fp8_matrix": [_P, _P, _Z, _P],

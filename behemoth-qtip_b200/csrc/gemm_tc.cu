@@ -34,7 +34,7 @@ constexpr size_t kTcSmemBytes = 1024 /*alignment slack*/ + size_t(kTcStages) * (
 
 __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
-                                                                float* __restrict__ z, int stride, int k_steps, int tokens,
+                                                                float* __restrict__ z, int stride, int k_total, int tokens,
                                                                 int out, int* __restrict__ status) {
   extern __shared__ unsigned char tc_smem_raw[];
   const uint32_t raw = smem_u32(tc_smem_raw);
@@ -43,6 +43,10 @@ __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_kernel(const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = blockIdx.x * (kTcHalves * kTcM), tok0 = blockIdx.y * kTcN;
   const int halves = min(kTcHalves, (out - row0) / kTcM);  // 1 for the last tile when out / 128 is odd
+  // K-split blockIdx.z of gridDim.z: its slice of the K steps and its slice [split][token][stride] of z
+  const int ks_lo = int(long(k_total) * blockIdx.z / gridDim.z);
+  const int k_steps = int(long(k_total) * (blockIdx.z + 1) / gridDim.z) - ks_lo;
+  z += size_t(blockIdx.z) * tokens * stride;
   volatile int* abort_flag = &sm.abort_flag;
 
   if (threadIdx.x == 0) {
@@ -74,8 +78,8 @@ __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_kernel(const __grid_con
       tc_mbar_expect_tx(bar, uint32_t(halves) * (kTcABytes / kTcHalves) + kTcBBytes);
       const uint32_t a_dst = tiles + uint32_t(s) * (kTcABytes + kTcBBytes);
       for (int h = 0; h < halves; ++h)
-        tc_tma_load_2d(a_dst + uint32_t(h) * (kTcABytes / kTcHalves), &map_w, k * kTcK, row0 + h * kTcM, bar);
-      tc_tma_load_2d(a_dst + kTcABytes, &map_x, k * kTcK, tok0, bar);
+        tc_tma_load_2d(a_dst + uint32_t(h) * (kTcABytes / kTcHalves), &map_w, (ks_lo + k) * kTcK, row0 + h * kTcM, bar);
+      tc_tma_load_2d(a_dst + kTcABytes, &map_x, (ks_lo + k) * kTcK, tok0, bar);
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer
@@ -174,23 +178,35 @@ int gemm_tc_device_setup() {
 
 using namespace qb;
 
-extern "C" int qtip_prefill_gemm(const uint16_t* w_dense_d, const uint16_t* x_d, float* z_d, int stride, int in, int out,
-                                 int tokens, int* status_d, void* stream) {
-  QB_REQUIRE(w_dense_d && x_d && z_d && tokens >= 1, QTIP_E_ARG, "qtip_prefill_gemm: bad argument");
+static int prefill_gemm_impl(const uint16_t* w_dense_d, const uint16_t* x_d, float* z_d, int stride, int in, int out,
+                             int tokens, int splits, int* status_d, void* stream, const char* who) {
+  QB_REQUIRE(w_dense_d && x_d && z_d && tokens >= 1, QTIP_E_ARG, "%s: bad argument", who);
   QB_REQUIRE(in > 0 && out > 0 && in % kTcK == 0 && out % kTcM == 0 && stride >= out, QTIP_E_GEOMETRY,
-             "qtip_prefill_gemm: in = %d must be a multiple of %d, out = %d of %d, stride >= out", in, kTcK, out, kTcM);
+             "%s: in = %d must be a multiple of %d, out = %d of %d, stride >= out", who, in, kTcK, out, kTcM);
+  QB_REQUIRE(splits >= 1 && splits <= in / kTcK && splits <= 65535, QTIP_E_GEOMETRY,
+             "%s: %d K-splits for %d K steps", who, splits, in / kTcK);
   QB_REQUIRE((reinterpret_cast<uintptr_t>(w_dense_d) | reinterpret_cast<uintptr_t>(x_d)) % 16 == 0, QTIP_E_ARG,
-             "qtip_prefill_gemm: operands must be 16-byte aligned");
+             "%s: operands must be 16-byte aligned", who);
   if (!device_info()) return QTIP_E_DEVICE;
   CUtensorMap map_w, map_x;
   int rc = tc_make_map(&map_w, w_dense_d, uint64_t(out), uint64_t(in), kTcM);
   if (rc) return rc;
   rc = tc_make_map(&map_x, x_d, uint64_t(tokens), uint64_t(in), kTcN);
   if (rc) return rc;
-  const dim3 grid((out / kTcM + kTcHalves - 1) / kTcHalves, (tokens + kTcN - 1) / kTcN);
-  QB_REQUIRE(grid.y <= 65535, QTIP_E_GEOMETRY, "qtip_prefill_gemm: too many tokens (%d)", tokens);
+  const dim3 grid((out / kTcM + kTcHalves - 1) / kTcHalves, (tokens + kTcN - 1) / kTcN, splits);
+  QB_REQUIRE(grid.y <= 65535, QTIP_E_GEOMETRY, "%s: too many tokens (%d)", who, tokens);
   gemm_tc_kernel<<<grid, kTcThreads, kTcSmemBytes, as_stream(stream)>>>(map_w, map_x, z_d, stride, in / kTcK, tokens,
                                                                         out, status_d);
   QB_LAUNCHED();
   return QTIP_OK;
+}
+
+extern "C" int qtip_prefill_gemm(const uint16_t* w_dense_d, const uint16_t* x_d, float* z_d, int stride, int in, int out,
+                                 int tokens, int* status_d, void* stream) {
+  return prefill_gemm_impl(w_dense_d, x_d, z_d, stride, in, out, tokens, 1, status_d, stream, "qtip_prefill_gemm");
+}
+extern "C" int qtip_prefill_gemm_splitk(const uint16_t* w_dense_d, const uint16_t* x_d, float* z_d, int stride, int in,
+                                        int out, int tokens, int splits, int* status_d, void* stream) {
+  return prefill_gemm_impl(w_dense_d, x_d, z_d, stride, in, out, tokens, splits, status_d, stream,
+                           "qtip_prefill_gemm_splitk");
 }

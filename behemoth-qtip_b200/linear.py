@@ -136,10 +136,26 @@ def qtip_multiply_prefill(w, x, z, stride, tokens, dense_scratch, status=None):
     prefill_gemm(dense_scratch, x, z, stride, w.n_in, w.n_out, tokens, status)
 
 
-def fp8_forward_prefill(w, scale, x, y, n_in, n_out, tokens, dense_scratch, z):
-    """FP8 K/V projection for prefill-sized batches on the tensor cores: exact bf16 copy of the weights, tcgen05 product
-    into z [tokens, out] f32, per-row scale and bf16 rounding (the reference's decode_fp8_matrix path)."""
+def prefill_gemm_splitk(w_dense, x, z, stride, n_in, n_out, tokens, splits, status=None):
+    """prefill_gemm with the K range split over the grid: z [splits, tokens, stride] f32 partial sums."""
     init()
+    lib().call("qtip_prefill_gemm_splitk", _p(w_dense, torch.bfloat16), _p(x, torch.bfloat16), _p(z, torch.float32),
+               stride, n_in, n_out, tokens, splits, _p(status, torch.int32), _stream())
+
+
+def fp8_splits(n_in, n_out, tokens, sm_count=148):
+    """K-splits that give the tensor-core product of a few-row weight about one CTA per SM."""
+    tiles = -(-n_out // 256) * -(-tokens // 256)
+    return max(1, min(n_in // 64 // 4, sm_count // tiles))
+
+
+def fp8_forward_prefill(w, scale, x, y, n_in, n_out, tokens, dense_scratch, z, splits=None):
+    """FP8 K/V projection for batches of tokens on the tensor cores: exact bf16 copy of the weights, tcgen05 product with
+    the K range split over the SMs into z [splits, tokens, out] f32, then the sum of the partials, the per-row scale and
+    the bf16 rounding (the reference's decode_fp8_matrix path)."""
+    init()
+    if splits is None:
+        splits = fp8_splits(n_in, n_out, tokens)
     lib().call("qtip_decode_fp8_matrix", _p(w, torch.uint8), _p(dense_scratch, torch.bfloat16), n_in * n_out, _stream())
-    prefill_gemm(dense_scratch, x, z, n_out, n_in, n_out, tokens)
-    reduce_to_b16(z, scale, y, tokens * n_out, n_out, 1)
+    prefill_gemm_splitk(dense_scratch, x, z, n_out, n_in, n_out, tokens, splits)
+    reduce_to_b16(z, scale, y, tokens * n_out, n_out, splits)

@@ -612,7 +612,7 @@ def layer_workload_tp(args):
                 dist.all_gather_into_tensor(zg, zl[:T * rows])
                 linear.qtip_finish(w, zg, ys[n_out], scratch, name in ("gate", "up"), 1, T, world)
             for w in w8:
-                if T >= 128:
+                if T >= 8:
                     linear.fp8_forward_prefill(w, s8, xs[hidden], ykv_l, hidden, kv_rows, T, dense[:kv_rows * hidden], z_l)
                 else:
                     linear.fp8_forward(w, s8, xs[hidden], ykv_l, hidden, kv_rows, T)
@@ -712,7 +712,7 @@ def layer_workload(args):
                     linear.qtip_multiply_batch(w, rot[n_in], z, n_out, sp, T)
                 linear.qtip_finish(w, z, ys[n_out], scratch, name in ("gate", "up"), sp, T)
             for w in w8:
-                if T >= 128:
+                if T >= 8:  # tensor cores with the K range split over the SMs; below that the streaming SIMT kernel
                     linear.fp8_forward_prefill(w, s8, xs[hidden], ys[kv], hidden, kv, T, dense[:kv * hidden], z)
                 else:
                     linear.fp8_forward(w, s8, xs[hidden], ys[kv], hidden, kv, T)

@@ -232,6 +232,11 @@ int qtip_reduce_to_b16(const float* x_d, const float* scale_d, uint16_t* y_d, si
  * Replaces the cublasGemmEx call of the >= 128-token path (runtime/cuda/tensor_model.cpp:210-222). */
 int qtip_prefill_gemm(const uint16_t* w_dense_d, const uint16_t* x_d, float* z_d, int stride, int in, int out, int tokens,
                       int* status_d, void* stream);
+/* The same product with the K range split `splits` ways over the grid, for weights with few rows (the FP8 K/V
+ * projections: 1,024 rows are 4 row tiles): z_d[(split * tokens + token) * stride + row] holds the partial sums, to be
+ * added by qtip_reduce_to_b16 / qtip_reduce_products / qtip_finish. */
+int qtip_prefill_gemm_splitk(const uint16_t* w_dense_d, const uint16_t* x_d, float* z_d, int stride, int in, int out,
+                             int tokens, int splits, int* status_d, void* stream);
 
 /* Products for 17 .. a few hundred tokens with the decode fused into the tcgen05 product: the codes are decoded straight
  * into the shared-memory A operand (no dense copy of the weights), 128 rows x 64/128/256 tokens per CTA, K split

@@ -179,10 +179,13 @@ def test_fp8_kv_projection(gpu, oracle, tokens):
     if tokens == 19 and n_out % 128 != 0:  # tensor-core variant needs out % 128 == 0: take the first 128 rows
         wd = torch.from_numpy(np.ascontiguousarray(w[:128])).cuda()
         dense = torch.empty((128, n_in), dtype=torch.bfloat16, device="cuda")
-        z = torch.empty((tokens, 128), dtype=torch.float32, device="cuda")
         y2 = torch.empty((tokens, 128), dtype=torch.bfloat16, device="cuda")
-        gpu.linear.fp8_forward_prefill(wd, dev(scale[:128]), bf16_dev(xb), y2, n_in, 128, tokens, dense, z)
-        assert rel_l2(y2.float().cpu().numpy(), ref_b[:, :128]) < 4e-3
+        for splits in (1, 5, None):  # None: the K range spread over the SMs (here 6 K-splits of 4 steps)
+            sp = splits or gpu.linear.fp8_splits(n_in, 128, tokens)
+            z = torch.full((sp, tokens, 128), float("nan"), dtype=torch.float32, device="cuda")
+            y2.zero_()
+            gpu.linear.fp8_forward_prefill(wd, dev(scale[:128]), bf16_dev(xb), y2, n_in, 128, tokens, dense, z, splits)
+            assert rel_l2(y2.float().cpu().numpy(), ref_b[:, :128]) < 4e-3
 
 
 @pytest.mark.parametrize("n_in,n_out,tokens", [(512, 256, 300), (1024, 128, 256), (12288, 384, 17)])
