@@ -43,7 +43,7 @@ int qtip_init(void);
  * Codebook. tlut_h: [512][2] fp16 bits on the HOST (the checkpoint's `tlut` tensor).
  */
 /* Encoder table: lut_h2_d[65536] packed half2 (lo = component 0) by quantlut_sym; *lut_rms_h (may be NULL) gets
- * sqrt(mean(lut^2)) in fp64. Synchronous host computation + one async H2D copy from an internal pinned buffer.
+ * sqrt(mean(lut^2)) in fp64. Synchronous host computation + one H2D copy of the table (the call returns after the copy has been issued from pageable memory, i.e. the host buffer may be reused).
  * Replaces build_codebook()/device_lut() (src/qtip_core.cpp:18-50, src/quantizer.cpp:14-28), with the table as a
  * parameter instead of a compiled-in constant. */
 int qtip_encoder_lut(const uint16_t* tlut_h, uint32_t* lut_h2_d, double* lut_rms_h, void* stream);
