@@ -39,3 +39,26 @@ def test_argument_checks_need_no_device(pkg):
     assert lib.cdll.qtip_ldlq(C.c_void_p(16), C.c_void_p(16), 100, 64, 0, 64, C.c_void_p(16), C.c_void_p(16),
                               C.c_void_p(16), C.c_void_p(16), 1 << 20, None) == -2
     assert lib.cdll.qtip_quantize_workspace_bytes(8) >= 8 * 16 * 4096 * 4
+
+
+def test_size_queries_and_host_heuristics(pkg):
+    """Workspace / exchange sizes and the K-split heuristics of the host mirror: pure host logic, no device."""
+    import ctypes as C
+    lib = pkg.Library()
+    ex = lib.cdll.qtip_tp_exchange_bytes
+    one = ex(57344, 1, 1)
+    assert one == 256 + 2 * ((57344 * 4 + 255) // 256 * 256)          # control block + two slots
+    assert ex(57344, 16, 4) == 256 + 2 * 57344 * 16 * 4 * 4
+    assert ex(0, 1, 1) == 0
+    ldlq = lib.cdll.qtip_ldlq_workspace_bytes(28672, 12288)
+    assert ldlq >= 28672 * 12288 * 4 + 768 * 16 * 4096 * 4                # prod + back-pointers of every sequence
+    assert lib.cdll.qtip_quantize_linear_workspace_bytes(12288, 28672) > ldlq
+    assert C.sizeof(pkg.QtipTpExchange) == 8 * 8 + 8 + 4 + 4 and C.sizeof(pkg.QtipMatrix) == 4 * 8 + 4 + 4
+    lin = pkg.linear
+    assert lin.tc_splits(12288) == 3 and lin.tc_splits(57344) == 4 and lin.tc_splits(128) == 4
+    assert lin.fp8_splits(12288, 1024, 64) == 37 and lin.fp8_splits(12288, 1024, 2048) == 4
+    assert lin.fp8_splits(1536, 128, 19) == 6
+    # exchange argument checks that need no device: bad rank count, bad slot
+    bad = pkg.QtipTpExchange()
+    bad.ranks, bad.rank, bad.bytes = 9, 0, 4096
+    assert lib.cdll.qtip_gathered_products(C.byref(bad), 0, C.byref(C.c_void_p())) == -1
