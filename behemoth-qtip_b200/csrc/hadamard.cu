@@ -13,6 +13,8 @@
 // products summed over K-splits, optionally rounded to bf16 -> times SV -> bf16 (operator output); bf16 z -> same.
 #include <cmath>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace qb {
@@ -367,7 +369,18 @@ static int launch(const HadArgs& a, long rows, bool force_row, cudaStream_t s) {
   } else {
     QB_REQUIRE(a.n <= kMaxRowFloats, QTIP_E_GEOMETRY, "Hadamard rows longer than %d are not supported (n = %d)",
                kMaxRowFloats, a.n);
-    had_row_kernel<K, T, M><<<unsigned(rows), 1024, size_t(a.n) * 4, s>>>(a);
+    // Rows that leave room for several CTAs per SM run with fewer threads per row once there are rows for every SM:
+    // the load, transform and store phases of different rows then overlap on each SM. Measured on 12288-wide fp32 rows:
+    // 3.3 TB/s with 1,024 threads (one row per SM), 4.2 with 512 (two), 4.7 with 256 (four); the output transforms
+    // (several partial sums per element) and 28,672-wide rows are best with 512.
+    static const int forced = [] { const char* e = std::getenv("QTIP_HAD_ROW_THREADS"); return e ? std::atoi(e) : 0; }();
+    constexpr bool kLight = M == Mode::F32Inplace || M == Mode::Prepare;
+    const size_t row_bytes = size_t(a.n) * 4, room = size_t(224) * 1024;
+    int row_threads = 1024;
+    if (rows >= 148 && row_bytes * 2 <= room) row_threads = 512;
+    if (kLight && rows >= 4 * 148 && row_bytes * 4 <= room) row_threads = 256;
+    if (forced == 256 || forced == 512 || forced == 1024) row_threads = forced;
+    had_row_kernel<K, T, M><<<unsigned(rows), row_threads, size_t(a.n) * 4, s>>>(a);
   }
   QB_LAUNCHED();
   return QTIP_OK;
