@@ -30,9 +30,8 @@
 
 namespace qb {
 
-constexpr int kFtRows = 128, kFtK = 64, kFtDecoders = 16, kFtEpilogueWarps = 4;
+constexpr int kFtRows = 128, kFtDecoders = 16, kFtEpilogueWarps = 4;
 constexpr int kFtThreads = (kFtDecoders + 2 + kFtEpilogueWarps) * 32;
-constexpr uint32_t kFtABytes = kFtRows * kFtK * 2;  // 16 KiB per stage
 constexpr int kFtLutBytes = 1024 * 32 * 4;         // 32 copies of the table
 constexpr int kFtMaxStages = 8;
 
@@ -43,10 +42,19 @@ struct FtSmem {
 };
 // One ring: a stage holds the decoded A tile and the activation tile of a K step, filled behind ONE barrier (the arrivals
 // of the group's decoder warps plus the TMA's transaction bytes) and released by ONE tcgen05.commit, so the single MMA
-// thread runs one wait and one commit per step. Stages = decoder groups: 4 (64 tokens), 2 (128 or 256 tokens).
-static int ft_stages(int n_tile) { return n_tile <= 64 ? 4 : 2; }
-static size_t ft_smem(int n_tile) {
-  return 1024 + kFtLutBytes + size_t(ft_stages(n_tile)) * (kFtABytes + size_t(n_tile) * kFtK * 2) + sizeof(FtSmem);
+// thread runs one wait and one commit per step. A K step is KB blocks of 32 columns; stages = decoder groups = G.
+// 64-token tiles: 128-column steps, two stages (fewer, larger steps: 229 us against 264 us with 64-column steps and
+// four stages on 57344 x 12288); 128- and 256-token tiles: 64-column steps, two stages (96 KiB of stages in all cases).
+struct FtConfig {
+  int groups, kblk;
+};
+static FtConfig ft_config(int n_tile, int n_in) {
+  if (n_tile <= 64) return n_in % 128 == 0 ? FtConfig{2, 4} : FtConfig{4, 2};
+  return FtConfig{2, 2};
+}
+static size_t ft_smem(int n_tile, FtConfig c) {
+  return 1024 + kFtLutBytes + size_t(c.groups) * (size_t(kFtRows) * 32 * c.kblk * 2 + size_t(n_tile) * 32 * c.kblk * 2) +
+         sizeof(FtSmem);
 }
 
 __device__ int g_ft_status;  // used when the caller passes no status word
@@ -104,11 +112,13 @@ struct FtWalk {
 };
 
 // Persistent: grid = min(SMs, items); CTA c takes items c, c + grid, ... z[(split * tokens + token) * stride + row].
-// G = decoder groups = stages of the ring.
-template <int G>
+// G = decoder groups = stages of the ring, KB = 32-column blocks per K step.
+template <int G, int KB>
 __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w, const __grid_constant__ CUtensorMap map_x,
                                                                    float* __restrict__ z, int stride, int tokens, int n_tile,
                                                                    int splits, int n_items, int* __restrict__ status) {
+  constexpr int kFtKblk = KB, kFtK = 32 * KB;
+  constexpr uint32_t kFtABytes = kFtRows * kFtK * 2;  // 16 or 32 KiB per stage
   const uint32_t raw = smem_u32(ft_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1,024-byte alignment
   unsigned char* smem = ft_smem_raw + (base - raw);
@@ -157,7 +167,7 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
   if (warp < kFtDecoders) {
     // ---- decoders: G groups of 16 / G warps; group g decodes the steps gk = g (mod G) into stage g, so G steps are in
     // the making at any time and a warp meets a barrier once per G / 2 whole 32 x 32 blocks.
-    constexpr int kWpg = kFtDecoders / G, kBpw = 8 / kWpg;  // warps per group, blocks per warp and step (G / 2)
+    constexpr int kWpg = kFtDecoders / G, kBpw = 4 * kFtKblk / kWpg;  // warps per group, blocks per warp and step
     const int grp = warp / kWpg, mem = warp % kWpg;
     const int n2 = w.in / 32;
     const uint32_t a_tile = a_ring + uint32_t(grp) * kFtABytes;
@@ -167,8 +177,8 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
     int brl[kBpw], kbl[kBpw];
 #pragma unroll
     for (int i = 0; i < kBpw; ++i) {
-      const int blk = mem * kBpw + i;  // block of the step: block-row blk >> 1, column block blk & 1
-      brl[i] = blk >> 1, kbl[i] = blk & 1;
+      const int blk = mem * kBpw + i;  // block of the step: block-row blk / kFtKblk, column block blk % kFtKblk
+      brl[i] = blk / kFtKblk, kbl[i] = blk % kFtKblk;
     }
     const uint2* codes = reinterpret_cast<const uint2*>(w.trellis) + lane;
     auto fetch = [&](const FtWalk& wk, uint2(&dst)[kBpw]) {
@@ -177,7 +187,7 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
       const bool live = !x.done();
       const int ks = live ? x.cur.ks_lo + x.k() : 0, r0 = live ? x.cur.row0 / 32 : 0;
 #pragma unroll
-      for (int i = 0; i < kBpw; ++i) dst[i] = codes[(size_t(r0 + brl[i]) * n2 + 2 * ks + kbl[i]) * 32];
+      for (int i = 0; i < kBpw; ++i) dst[i] = codes[(size_t(r0 + brl[i]) * n2 + kFtKblk * ks + kbl[i]) * 32];
     };
     constexpr int kAhead = 4;  // group steps of codes in flight per lane (= 4 G K steps)
     uint2 next[kAhead][kBpw];
@@ -222,7 +232,8 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
                 a[t] = lut_s[((y >> 6) & 1023u) * 32u + lane];
               }
               const int r = brl[i] * 32 + i1 * 16 + lrow, ch = kbl[i] * 4 + j1 * 2 + lchunk;
-              stmatrix_x4(a_tile + uint32_t(r) * 128u + (uint32_t(ch ^ (r & 7)) << 4), a[0], a[1], a[2], a[3]);
+              stmatrix_x4(a_tile + uint32_t(ch >> 3) * 16384u + uint32_t(r) * 128u + (uint32_t((ch & 7) ^ (r & 7)) << 4),
+                          a[0], a[1], a[2], a[3]);
             }
           }
         }
@@ -242,7 +253,9 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
         if (uses >= 1 && !tc_wait(smem_u32(&sm.empty[s]), uint32_t((uses - 1) & 1), abort_flag, status)) break;
         const uint32_t bar = smem_u32(&sm.full[s]);
         tc_mbar_expect_tx(bar, b_bytes);
-        tc_tma_load_2d(b_ring + uint32_t(s) * b_bytes, &map_x, (wk.cur.ks_lo + wk.k()) * kFtK, wk.cur.tok0, bar);
+        for (int sub = 0; sub < kFtKblk / 2; ++sub)  // one 64-column box per 128-byte-swizzled sub-tile
+          tc_tma_load_2d(b_ring + uint32_t(s) * b_bytes + uint32_t(sub) * uint32_t(n_tile) * 128u, &map_x,
+                         (wk.cur.ks_lo + wk.k()) * kFtK + 64 * sub, wk.cur.tok0, bar);
       }
     }
   } else if (warp == kFtDecoders + 1) {
@@ -263,12 +276,15 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
           ok = tc_wait(smem_u32(&sm.full[s]), uint32_t((wk.gk / G) & 1), abort_flag, status);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint64_t a_desc = tc_smem_desc(a_ring + uint32_t(s) * kFtABytes);
-          const uint64_t b_desc = tc_smem_desc(b_ring + uint32_t(s) * b_bytes);
 #pragma unroll
-          for (int kk = 0; kk < kFtK / 16; ++kk)
-            tc_mma(tmem + uint32_t(buf * n_tile), a_desc + uint64_t(2 * kk), b_desc + uint64_t(2 * kk), idesc,
-                   k > 0 || kk > 0);
+          for (int sub = 0; sub < kFtKblk / 2; ++sub) {
+            const uint64_t a_desc = tc_smem_desc(a_ring + uint32_t(s) * kFtABytes + uint32_t(sub) * 16384u);
+            const uint64_t b_desc = tc_smem_desc(b_ring + uint32_t(s) * b_bytes + uint32_t(sub) * uint32_t(n_tile) * 128u);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              tc_mma(tmem + uint32_t(buf * n_tile), a_desc + uint64_t(2 * kk), b_desc + uint64_t(2 * kk), idesc,
+                     k > 0 || kk > 0 || sub > 0);
+          }
           tc_commit(smem_u32(&sm.empty[s]));
           wk.advance(1);
         }
@@ -322,8 +338,10 @@ __global__ __launch_bounds__(kFtThreads, 1) void trellis_tc_kernel(qtip_matrix w
 }
 
 int trellis_tc_device_setup() {
-  QB_CUDA(cudaFuncSetAttribute(trellis_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ft_smem(256))));
-  QB_CUDA(cudaFuncSetAttribute(trellis_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ft_smem(64))));
+  const int big = int(ft_smem(256, FtConfig{2, 2}));  // every configuration stays within this size
+  QB_CUDA(cudaFuncSetAttribute(trellis_tc_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  QB_CUDA(cudaFuncSetAttribute(trellis_tc_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  QB_CUDA(cudaFuncSetAttribute(trellis_tc_kernel<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   return QTIP_OK;
 }
 
@@ -332,7 +350,7 @@ static int ft_token_tile(int tokens) { return tokens <= 64 ? 64 : (tokens <= 128
 
 int trellis_tc_multiply(qtip_matrix w, const uint16_t* x, float* z, int stride, int splits, int tokens, int* status,
                         cudaStream_t s) {
-  QB_REQUIRE(w.in % kFtK == 0 && w.out % kFtRows == 0, QTIP_E_GEOMETRY,
+  QB_REQUIRE(w.in % 64 == 0 && w.out % kFtRows == 0, QTIP_E_GEOMETRY,
              "the fused tensor-core product needs in %% 64 == 0 and out %% 128 == 0 (in = %d, out = %d)", w.in, w.out);
   QB_REQUIRE(reinterpret_cast<uintptr_t>(x) % 16 == 0, QTIP_E_ARG, "activations must be 16-byte aligned");
   const int n_tile = ft_token_tile(tokens);
@@ -347,18 +365,20 @@ int trellis_tc_multiply(qtip_matrix w, const uint16_t* x, float* z, int stride, 
   const DeviceInfo* info = device_info();
   if (!info) return QTIP_E_DEVICE;
   // More K-splits than K steps: the surplus slices of z hold zeros, the kernel runs with one step per split.
-  const int k_total = w.in / kFtK, eff = splits < k_total ? splits : k_total;
+  const FtConfig cfg = ft_config(n_tile, w.in);
+  const int k_total = w.in / (32 * cfg.kblk), eff = splits < k_total ? splits : k_total;
   if (eff < splits)
     QB_CUDA(cudaMemsetAsync(z + size_t(eff) * tokens * stride, 0, size_t(splits - eff) * tokens * stride * sizeof(float), s));
   const long items = long(w.out / kFtRows) * ((tokens + n_tile - 1) / n_tile) * eff;
   QB_REQUIRE(items < (1l << 30), QTIP_E_GEOMETRY, "too many work items (%ld)", items);
   const int grid = int(items < info->sm_count ? items : info->sm_count);
-  if (ft_stages(n_tile) == 4)
-    trellis_tc_kernel<4><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile, eff, int(items),
-                                                                   status);
+  const size_t smem = ft_smem(n_tile, cfg);
+  if (cfg.groups == 2 && cfg.kblk == 4)
+    trellis_tc_kernel<2, 4><<<grid, kFtThreads, smem, s>>>(w, map_x, z, stride, tokens, n_tile, eff, int(items), status);
+  else if (cfg.groups == 4)
+    trellis_tc_kernel<4, 2><<<grid, kFtThreads, smem, s>>>(w, map_x, z, stride, tokens, n_tile, eff, int(items), status);
   else
-    trellis_tc_kernel<2><<<grid, kFtThreads, ft_smem(n_tile), s>>>(w, map_x, z, stride, tokens, n_tile, eff, int(items),
-                                                                   status);
+    trellis_tc_kernel<2, 2><<<grid, kFtThreads, smem, s>>>(w, map_x, z, stride, tokens, n_tile, eff, int(items), status);
   QB_LAUNCHED();
   return QTIP_OK;
 }
