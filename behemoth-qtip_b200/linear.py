@@ -94,6 +94,11 @@ def tc_splits(n_out, sm_count=148, max_splits=4):
     return min(range(1, max_splits + 1), key=lambda sp: (-(-tiles * sp // sm_count) / sp, sp))
 
 
+def batch_uses_tc(n_in, n_out, tokens):
+    """The rule by which qtip_multiply_batch (implementation = -1) takes the fused tensor-core kernel."""
+    return n_in % 64 == 0 and n_out % 128 == 0 and (tokens > 16 or (tokens > 8 and n_out <= 16384))
+
+
 def kernel_status():
     """Synchronises; raises QtipError if a tensor-core kernel without a status word reported a time-out."""
     lib().call("qtip_kernel_status", _stream())

@@ -693,10 +693,12 @@ def layer_workload(args):
         xs = {n: torch.randn(T, n, generator=g, device="cuda").to(torch.bfloat16) for n in (hidden, inter)}
         rot = {n: torch.empty(T, n, dtype=torch.bfloat16, device="cuda") for n in (hidden, inter)}
         ys = {n: torch.empty(T, n, dtype=torch.bfloat16, device="cuda") for n in (hidden, inter, kv)}
-        if 16 < T <= 512:
-            splits = {name: linear.tc_splits(shapes[name][1]) for name in shapes}
-        else:
-            splits = {name: (2 if (T <= 16 and shapes[name][1] == hidden) else 1) for name in shapes}
+        splits = {}
+        for name, (n_in, n_out) in shapes.items():
+            if T <= 512 and linear.batch_uses_tc(n_in, n_out, T):
+                splits[name] = linear.tc_splits(n_out)
+            else:
+                splits[name] = 2 if (T <= 16 and n_out == hidden) else 1
         z = torch.empty(4 * T * inter if T <= 512 else T * inter, dtype=torch.float32, device="cuda")
         scratch = torch.empty(1, dtype=torch.float32, device="cuda")
 

@@ -243,7 +243,8 @@ int qtip_prefill_gemm_splitk(const uint16_t* w_dense_d, const uint16_t* x_d, flo
  * `splits` ways (z_d[(split * tokens + token) * stride + row], summed by qtip_finish / qtip_reduce_products). Needs
  * in % 64 == 0 and out % 128 == 0. status_d (one int, may be NULL: then a word inside the library, read by
  * qtip_kernel_status) is set to 2 if a bounded pipeline wait timed out. qtip_multiply_batch takes this path by itself
- * above 16 tokens (implementation = 0 keeps the 16-tokens-per-pass kernel, 2 forces this one). Takes the place of the
+ * above 16 tokens, and from 9 tokens for matrices of up to 16,384 rows (implementation = 0 keeps the 16-tokens-per-pass
+ * kernel, 2 forces this one). Takes the place of the
  * 17..127-token kernel of runtime/cuda/batch_kernels.cu:23-288 (launch<0>) and, up to a few hundred tokens, of the dense
  * decode + library GEMM of runtime/cuda/tensor_model.cpp:210-222. */
 int qtip_multiply_tc(qtip_matrix w, const uint16_t* rotated_d, float* z_d, int stride, int splits, int tokens,
