@@ -132,7 +132,7 @@ static int ldlq_slices(long ntr) {
     const int v = std::atoi(e);
     if (v >= 1 && v <= kMaxSlices) return ntr >= v ? v : 1;
   }
-  return ntr >= 256 ? 2 : 1;
+  return ntr >= 128 ? 2 : 1;  // measured: 192 sequences per step 2.13 s -> 1.64 s, 768: 7.0 -> 5.97 s, 96: no difference
 }
 static size_t slice_ws_bytes(long ntr, int slices) {  // Viterbi scratch of all slices together
   size_t total = 0;
