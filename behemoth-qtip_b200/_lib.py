@@ -37,7 +37,6 @@ SIGNATURES = {
     "qtip_runtime_lut": [_P, _P, _P],
     "qtip_k_ldlq_prep": [_P, _P, _P, _P, _L, _L, _I, _I, _P, _P],
     "qtip_k_viterbi_fwd": [_P, _P, _I, _I, _P, _P, _P, _P],
-    "qtip_k_viterbi_fwd_simple": [_P, _P, _I, _I, _P, _P, _P, _P],
     "qtip_k_viterbi_overlap": [_P, _P, _I, _P, _P],
     "qtip_k_viterbi_finish": [_P, _P, _I, _I, _P, _I, _I, _P, _L, _I, _P, _P],
     "qtip_k_decode_states": [_P, _I, _P, _P, _P],
@@ -79,6 +78,7 @@ SIGNATURES = {
     "qtip_prefill_gemm_splitk": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "qtip_multiply_tc": [QtipMatrix, _P, _P, _I, _I, _I, _P, _P],
     "qtip_kernel_status": [_P],
+    "qtip_debug_set_status": [_I, _I, _P],
     "qtip_decode_fp8_matrix": [_P, _P, _Z, _P],
     "qtip_fp8_forward": [_P, _P, _P, _P, _I, _I, _I, _P],
     "qtip_reduce_products": [_P, _Z, _I, _P],

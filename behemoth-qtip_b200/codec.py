@@ -69,13 +69,6 @@ def k_viterbi_fwd(X, overlap, roll, B, A, final_state, lut_h2):
                _p(final_state, torch.int16), _p(lut_h2, torch.int32), _stream())
 
 
-def k_viterbi_fwd_simple(X, overlap, roll, B, A, final_state, lut_h2):
-    """k_viterbi_fwd computed by the plain one-CTA-per-sequence kernel (cross-check implementation)."""
-    init()
-    lib().call("qtip_k_viterbi_fwd_simple", _p(X, torch.float32), _p(overlap, torch.int32), roll, B, _p(A, torch.int16),
-               _p(final_state, torch.int16), _p(lut_h2, torch.int32), _stream())
-
-
 def k_viterbi_overlap(A, final_state, B, overlap):
     init()
     lib().call("qtip_k_viterbi_overlap", _p(A, torch.int16), _p(final_state, torch.int16), B, _p(overlap, torch.int32),
@@ -177,13 +170,14 @@ def quantize_workspace(max_tiles):
     return Workspace(lib().raw("qtip_quantize_workspace_bytes")(int(max_tiles)))
 
 
-def quantize_tiles(X, lut_h2, states=None, hat=None, workspace=None):
-    """Two-pass tail-biting quantisation of X [B, 256] f32 -> (states int16 [B, 128], hat f32 [B, 256])."""
+def quantize_tiles(X, lut_h2, states=None, hat=None, workspace=None, want_hat=True):
+    """Two-pass tail-biting quantisation of X [B, 256] f32 -> (states int16 [B, 128], hat f32 [B, 256]); with
+    want_hat=False the decoded values are not written (the C ABI takes a null pointer) and None is returned for them."""
     init()
     B = X.shape[0]
     if states is None:
         states = torch.empty((B, 128), dtype=torch.int16, device=X.device)
-    if hat is None:
+    if hat is None and want_hat:
         hat = torch.empty((B, 256), dtype=torch.float32, device=X.device)
     if workspace is None:
         workspace = quantize_workspace(min(max(B, 8), 4608))

@@ -38,7 +38,9 @@ int viterbi_device_setup(DeviceInfo* info);  // viterbi.cu
 int decode_device_setup(DeviceInfo* info);   // decode.cu
 int gemm_tc_device_setup();                   // gemm_tc.cu
 int trellis_tc_device_setup();                // trellis_tc.cu
-int viterbi_read_status(int* value, cudaStream_t s);  // viterbi.cu: status word of kernel-level cluster launches
+// viterbi.cu: status words of the kernel-level cluster launches and of the built-in scratch; read, then cleared, on `s`
+int viterbi_read_status(int* kernel_level, int* noalloc, cudaStream_t s);
+int viterbi_set_status(int which, int value, cudaStream_t s);  // test hook behind qtip_debug_set_status
 int hadamard_device_setup();                 // hadamard.cu: uploads the order-12/20/28 factors
 
 // Order-K Hadamard factor (Paley construction), K in {12, 20, 28}; row-major +-1. Returns false otherwise.

@@ -54,20 +54,50 @@ __device__ __forceinline__ void warps_sync(int id, int warps) {
 // replicated LUT.
 extern __shared__ __align__(16) uint32_t gemm_smem_words[];
 
-// Decodes window u (word c << 16 | word c+1) into the four LUT words of states 4c..4c+3 from the replicated table
-// (entry e, copy l at word 32 e + l), so every lane reads its own bank. Bits above 15 of a shifted window do not reach
-// bits 6..15 of v (v + 1), which are the entry.
-// Decodes window u (word c << 16 | word c+1) into the four LUT words of states 4c..4c+3 from the replicated table
-// (entry e, copy l at word 32 e + l), so every lane reads its own bank. Bits above 15 of a shifted window do not reach
-// bits 6..15 of v (v + 1), which are the entry. (Other ways of forming the address -- mask then multiply-add, shift
-// then a three-input logic op, funnel shifts straight from the two source registers -- measured the same or slower.)
-__device__ __forceinline__ void decode_window(uint32_t u, uint32_t lane, uint32_t (&a)[4]) {
+// Decodes the two windows that one 32-bit word pair holds: o = word c of tiles (i1 = 1 : i1 = 0) of one tile column,
+// p = word c + 1 of the same tiles. State t of a window is its 16 bits starting at bit 4 t; bits above 15 of a state
+// register never reach the table index, so a state is cut with ONE funnel shift from the two source registers (the first
+// state of the low tile is `o` itself), doubled, hashed with one multiply-add (2 v (v + 1), entry in bits 7..16) and
+// turned into the byte address of the lane's own copy (entry e, copy l at byte 128 e + 4 l) with one three-input logic
+// operation: shift, add, multiply-add, and-or, load per state.
+#ifndef QB_GEMV_DECODE
+#define QB_GEMV_DECODE 1
+#endif
+__device__ __forceinline__ uint32_t lut_word(uint32_t v, uint32_t lane4) {
+#if QB_GEMV_DECODE == 1
+  const uint32_t v2 = v + v;
+  uint32_t y2;
+  asm("mad.lo.u32 %0, %1, %2, %2;" : "=r"(y2) : "r"(v), "r"(v2));
+  const uint32_t at = (y2 & 0x1ff80u) | lane4;
+#elif QB_GEMV_DECODE == 2
+  const uint32_t y = v * v + v;
+  const uint32_t at = ((y << 1) & 0x1ff80u) | lane4;
+#else
+  const uint32_t y = v * v + v;
+  const uint32_t at = (((y >> 6) & 1023u) << 7) + lane4;
+#endif
+#if defined(QB_GEMV_ABLATE) && QB_GEMV_ABLATE == 1
+  return at;
+#else
+  return *reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(gemm_smem_words) + at);
+#endif
+}
+__device__ __forceinline__ void decode_pair(uint32_t o, uint32_t p, uint32_t lane4, uint32_t (&lo)[4],
+                                            uint32_t (&hi)[4]) {
+#if QB_GEMV_DECODE == 0
+  const uint32_t u0 = __byte_perm(o, p, 0x1054), u1 = __byte_perm(o, p, 0x3276);
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const uint32_t v = u >> (16 - 4 * k);
-    const uint32_t y = v * v + v;
-    a[k] = gemm_smem_words[((y >> 6) & 1023u) * 32u + lane];
+  for (int k = 0; k < 4; ++k) lo[k] = lut_word(u0 >> (16 - 4 * k), lane4), hi[k] = lut_word(u1 >> (16 - 4 * k), lane4);
+#else
+  const uint32_t pl = p << 16, oh = o >> 16;
+  lo[0] = lut_word(o, lane4);
+  hi[0] = lut_word(oh, lane4);
+#pragma unroll
+  for (int k = 1; k < 4; ++k) {
+    lo[k] = lut_word(__funnelshift_l(pl, o, 4 * k), lane4);
+    hi[k] = lut_word(__funnelshift_l(p, oh, 4 * k), lane4);
   }
+#endif
 }
 
 // Tensor-parallel push: the products of this rank's rows go straight into every rank's gathered buffer (plain stores
@@ -103,6 +133,7 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, const TpPush& push, i
                                          float* red) {
   constexpr int RT = XS ? 1 : NT * 8;  // tokens kept per warp in the reduction buffer
   const int lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
+  const uint32_t lane4 = uint32_t(lane) * 4u;
   const int br = item / c.splits, sp = item - br * c.splits;
   const int k_lo = int(long(c.n2) * sp / c.splits), k_hi = int(long(c.n2) * (sp + 1) / c.splits);
   const int span = k_hi - k_lo;
@@ -122,7 +153,10 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, const TpPush& push, i
     // 16-byte load of words 4 tg .. 4 tg + 3 per token group and a 4 x 4 word transpose inside the quad (four shuffles).
     uint32_t bw[NT][4];
     if constexpr (XS) {
-      const uint4 xb = reinterpret_cast<const uint4*>(gemm_smem_words + c.xs_word)[blk * 4 + tg];
+      // One token is column 0 of the MMA's B operand, which lanes 0..3 supply; the other lanes' registers feed columns
+      // whose results are never read, so only the first quad loads (one 64-byte shared-memory wavefront, not four).
+      uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+      if (lane < 4) xb = reinterpret_cast<const uint4*>(gemm_smem_words + c.xs_word)[blk * 4 + tg];
       bw[0][0] = xb.x, bw[0][1] = xb.y, bw[0][2] = xb.z, bw[0][3] = xb.w;
     } else {
       const bool odd = tg & 1, hi = tg & 2;
@@ -142,44 +176,51 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, const TpPush& push, i
     }
 #pragma unroll
     for (int j1 = 0; j1 < 2; ++j1) {
-      uint32_t bf[NT][2];
+      uint32_t a[2][4];
+      decode_pair(j1 ? own.y : own.x, j1 ? peer.y : peer.x, lane4, a[0], a[1]);
 #pragma unroll
-      for (int t = 0; t < NT; ++t) bf[t][0] = bw[t][2 * j1], bf[t][1] = bw[t][2 * j1 + 1];
-      const uint32_t o = j1 ? own.y : own.x, p = j1 ? peer.y : peer.x;
+      for (int i1 = 0; i1 < 2; ++i1)
 #pragma unroll
-      for (int i1 = 0; i1 < 2; ++i1) {
-        uint32_t a[4];
-        decode_window(__byte_perm(o, p, i1 ? 0x3276 : 0x1054), uint32_t(lane), a);
-#pragma unroll
-        for (int t = 0; t < NT; ++t) mma_bf16_16816(acc[t][i1], a, bf[t][0], bf[t][1]);
-      }
+        for (int t = 0; t < NT; ++t) {
+#if defined(QB_GEMV_ABLATE) && QB_GEMV_ABLATE == 2
+          acc[t][i1][0] = __uint_as_float(__float_as_uint(acc[t][i1][0]) ^ a[i1][0] ^ a[i1][1] ^ a[i1][2] ^ a[i1][3] ^ bw[t][2 * j1]);
+#else
+          mma_bf16_16816(acc[t][i1], a[i1], bw[t][2 * j1], bw[t][2 * j1 + 1]);
+#endif
+        }
     }
   };
-  // Two register sets of kChunk blocks alternate: one is consumed while the loads of the other are in flight.
-  const unsigned off0 = unsigned(br) * unsigned(c.n2) * 32u + unsigned(lane);
-  auto fetch = [&](uint2(&dst)[kChunk], int first) {
+  // Two register sets of CH blocks alternate: one is consumed while the loads of the other are in flight. The main
+  // loop takes whole double chunks without per-block tests; what is left of the run (fewer than 2 CH blocks) goes
+  // block by block.
+  constexpr int CH = NT == 2 ? 2 : kChunk;  // 16 tokens keep twice the accumulators: shorter register sets
+  const uint2* mine = c.codes + (size_t(br) * size_t(c.n2) * 32u + unsigned(lane));
+  auto fetch = [&](uint2(&dst)[CH], int first) {
 #pragma unroll
-    for (int q = 0; q < kChunk; ++q) dst[q] = c.codes[off0 + unsigned(min(first + q, b_hi - 1)) * 32u];
+    for (int q = 0; q < CH; ++q) dst[q] = mine[unsigned(first + q) * 32u];
   };
-  auto consume = [&](const uint2(&src)[kChunk], int first) {
+  auto one = [&](uint2 own, int blk) {
+    process(own, make_uint2(__shfl_sync(0xffffffffu, own.x, (lane + 1) & 31),
+                            __shfl_sync(0xffffffffu, own.y, (lane + 1) & 31)), blk);
+  };
+  auto consume = [&](const uint2(&src)[CH], int first) {
 #pragma unroll
-    for (int q = 0; q < kChunk; ++q)
-      if (first + q < b_hi) {
-        const uint2 own = src[q];
-        process(own, make_uint2(__shfl_sync(0xffffffffu, own.x, (lane + 1) & 31),
-                                __shfl_sync(0xffffffffu, own.y, (lane + 1) & 31)), first + q);
-      }
+    for (int q = 0; q < CH; ++q) one(src[q], first + q);
   };
-  if (b_lo < b_hi) {
-    uint2 bufA[kChunk], bufB[kChunk];
-    fetch(bufA, b_lo);
-    for (int b0 = b_lo; b0 < b_hi; b0 += 2 * kChunk) {
-      if (b0 + kChunk < b_hi) fetch(bufB, b0 + kChunk);
-      consume(bufA, b0);
-      if (b0 + 2 * kChunk < b_hi) fetch(bufA, b0 + 2 * kChunk);
-      if (b0 + kChunk < b_hi) consume(bufB, b0 + kChunk);
+  int b = b_lo;
+  const int rounds = (b_hi - b_lo) / (2 * CH);
+  if (rounds > 0) {
+    uint2 bufA[CH], bufB[CH];
+    fetch(bufA, b);
+    for (int it = 0; it < rounds; ++it, b += 2 * CH) {
+      fetch(bufB, b + CH);
+      consume(bufA, b);
+      if (it + 1 < rounds) fetch(bufA, b + 2 * CH);
+      consume(bufB, b + CH);
     }
   }
+#pragma unroll 1
+  for (; b < b_hi; ++b) one(mine[unsigned(b) * 32u], b);
   // C fragment: c0 (row g, token 2tg), c1 (row g, token 2tg+1), c2 (row g+8, token 2tg), c3 (row g+8, token 2tg+1)
   float* wr = red + size_t(wi) * RT * 32;
   if constexpr (XS) {

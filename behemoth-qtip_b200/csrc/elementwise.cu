@@ -30,17 +30,22 @@ __global__ void sub_kernel(const float* A, const float* B, float* D, long rows, 
   }
 }
 
+// Sum of one double per thread over the CTA (at most 1,024 threads), valid in thread 0. Lanes fold with
+// __reduce-style butterfly steps on the two 32-bit halves; one slot per warp in shared memory carries the warp totals to
+// warp 0, which folds them the same way.
+__device__ __forceinline__ double warp_total(double v) {
+#pragma unroll
+  for (int step = 1; step < 32; step <<= 1) v += __shfl_down_sync(0xffffffffu, v, step);
+  return v;  // complete in lane 0
+}
 __device__ __forceinline__ double block_sum(double v) {
-  __shared__ double red[32];
-  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) red[w] = v;
+  __shared__ double warp_totals[32];
+  const int lane = threadIdx.x % 32, warp = threadIdx.x / 32, warps = (blockDim.x + 31) / 32;
+  v = warp_total(v);
+  if (lane == 0) warp_totals[warp] = v;
   __syncthreads();
-  const int nw = (blockDim.x + 31) >> 5;
-  v = (int(threadIdx.x) < nw) ? red[threadIdx.x] : 0.0;
-  if (w == 0)
-    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-  return v;
+  if (warp != 0) return 0.0;
+  return warp_total(lane < warps ? warp_totals[lane] : 0.0);
 }
 // out += sum over the block of A .* B (B == nullptr: A .* A); fp64 accumulation, one atomic per CTA.
 __global__ void dot_kernel(const float* A, long lda, const float* B, long ldb, long rows, long cols, double* out) {

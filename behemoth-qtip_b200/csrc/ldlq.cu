@@ -226,36 +226,44 @@ extern "C" int qtip_ldlq(const float* WT_d, const float* L_d, long n, long m, lo
     QB_CUDA(cudaEventRecord(side->fork, s));
     for (int i = 1; i < slices; ++i) QB_CUDA(cudaStreamWaitEvent(sl[i].st, side->fork, 0));
   }
-  for (long cur = n / 16; cur > 0; cur -= 8) {
-    const int bufend = int(16 * cur), c0 = bufend - 128;
-    for (int i = 7; i >= 0; --i) {
-      const int col0 = c0 + 16 * i;
-      for (int q = 0; q < slices; ++q) {  // the same column step of every slice, each on its own stream
-        const Slice& a = sl[q];
-        ldlq_prep_kernel<<<blocks_for(a.mj, 256), 256, 0, a.st>>>(WT_d, hatWT_d, prod, L_d, n, m, a.j0, a.mj, col0, bufend,
-                                                                 a.X);
-        QB_LAUNCHED();
-        int rc = quantize_tiles_impl(a.X, a.ntr, int(a.j0 / 16), lut_h2_d, Q_d, nblk, col0 / 16, nullptr, hatWT_d, m, col0,
-                                     a.vws, a.vws_bytes, false, a.st, false);
-        if (rc) return rc;
+  // The column loop as a function: a failed launch still passes the join below, so the side streams are never left
+  // running (or a stream capture left forked) behind an error return.
+  auto columns = [&]() -> int {
+    for (long cur = n / 16; cur > 0; cur -= 8) {
+      const int bufend = int(16 * cur), c0 = bufend - 128;
+      for (int i = 7; i >= 0; --i) {
+        const int col0 = c0 + 16 * i;
+        for (int q = 0; q < slices; ++q) {  // the same column step of every slice, each on its own stream
+          const Slice& a = sl[q];
+          ldlq_prep_kernel<<<blocks_for(a.mj, 256), 256, 0, a.st>>>(WT_d, hatWT_d, prod, L_d, n, m, a.j0, a.mj, col0,
+                                                                   bufend, a.X);
+          QB_LAUNCHED();
+          int rc = quantize_tiles_impl(a.X, a.ntr, int(a.j0 / 16), lut_h2_d, Q_d, nblk, col0 / 16, nullptr, hatWT_d, m,
+                                       col0, a.vws, a.vws_bytes, false, a.st, false);
+          if (rc) return rc;
+        }
+      }
+      if (c0 > 0) {
+        for (int q = 0; q < slices; ++q) {
+          const Slice& a = sl[q];
+          const dim3 grid(blocks_for(a.mj, kUpTile), blocks_for(c0, kUpTile));
+          ldlq_update_kernel<<<grid, 256, 0, a.st>>>(WT_d, hatWT_d, L_d, prod, n, m, a.j0, a.mj, c0);
+          QB_LAUNCHED();
+        }
       }
     }
-    if (c0 > 0) {
-      for (int q = 0; q < slices; ++q) {
-        const Slice& a = sl[q];
-        const dim3 grid(blocks_for(a.mj, kUpTile), blocks_for(c0, kUpTile));
-        ldlq_update_kernel<<<grid, 256, 0, a.st>>>(WT_d, hatWT_d, L_d, prod, n, m, a.j0, a.mj, c0);
-        QB_LAUNCHED();
-      }
-    }
-  }
+    return QTIP_OK;
+  };
+  const int rc_columns = columns();
   for (int i = 1; i < slices; ++i) {
     QB_CUDA(cudaEventRecord(side->join[i - 1], sl[i].st));
     QB_CUDA(cudaStreamWaitEvent(s, side->join[i - 1], 0));
-    merge_status_kernel<<<1, 1, 0, s>>>(static_cast<int*>(sl[0].vws), static_cast<const int*>(sl[i].vws));
-    QB_LAUNCHED();
+    if (rc_columns == QTIP_OK) {
+      merge_status_kernel<<<1, 1, 0, s>>>(static_cast<int*>(sl[0].vws), static_cast<const int*>(sl[i].vws));
+      QB_LAUNCHED();
+    }
   }
-  return QTIP_OK;
+  return rc_columns;
 }
 
 // ---------------------------------------------------------------- one linear of a Hessian group, end to end

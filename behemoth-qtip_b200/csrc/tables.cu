@@ -3,6 +3,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -26,6 +27,9 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
 
 static std::mutex g_mu;
 static DeviceInfo g_dev[64];
+// Published with release order after g_dev[dev] is complete and read with acquire order, so that a thread calling an
+// entry point while another thread initialises the device sees either "not ready" or the whole record.
+static std::atomic<bool> g_dev_ready[64];
 
 DeviceInfo* device_info() {
   int dev = -1;
@@ -33,7 +37,7 @@ DeviceInfo* device_info() {
     fail(QTIP_E_DEVICE, "no current CUDA device");
     return nullptr;
   }
-  if (!g_dev[dev].ready) {
+  if (!g_dev_ready[dev].load(std::memory_order_acquire)) {
     fail(QTIP_E_DEVICE, "qtip_init() has not been called on device %d", dev);
     return nullptr;
   }
@@ -124,7 +128,7 @@ extern "C" int qtip_init(void) {
   QB_CUDA(cudaGetDevice(&dev));
   QB_REQUIRE(dev >= 0 && dev < 64, QTIP_E_DEVICE, "device index %d out of range", dev);
   std::lock_guard<std::mutex> lk(g_mu);
-  if (g_dev[dev].ready) return QTIP_OK;
+  if (g_dev_ready[dev].load(std::memory_order_acquire)) return QTIP_OK;
   cudaDeviceProp prop{};
   QB_CUDA(cudaGetDeviceProperties(&prop, dev));
   QB_REQUIRE(prop.major == 10, QTIP_E_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", dev,
@@ -143,6 +147,7 @@ extern "C" int qtip_init(void) {
   if (rc) return rc;
   info.ready = true;
   g_dev[dev] = info;
+  g_dev_ready[dev].store(true, std::memory_order_release);
   return QTIP_OK;
 }
 

@@ -396,12 +396,26 @@ extern "C" int qtip_multiply_tc(qtip_matrix w, const uint16_t* rotated_d, float*
   return trellis_tc_multiply(w, rotated_d, z_d, stride, splits, tokens, status_d, as_stream(stream));
 }
 extern "C" int qtip_kernel_status(void* stream) {
-  int h = 0, v = 0;
-  QB_CUDA(cudaMemcpyFromSymbolAsync(&h, g_ft_status, sizeof h, 0, cudaMemcpyDeviceToHost, as_stream(stream)));
-  int rc = viterbi_read_status(&v, as_stream(stream));
+  int h = 0, v = 0, na = 0;
+  void* ft = nullptr;
+  QB_CUDA(cudaGetSymbolAddress(&ft, g_ft_status));
+  QB_CUDA(cudaMemcpyAsync(&h, ft, sizeof h, cudaMemcpyDeviceToHost, as_stream(stream)));
+  QB_CUDA(cudaMemsetAsync(ft, 0, sizeof h, as_stream(stream)));  // clear on read
+  int rc = viterbi_read_status(&v, &na, as_stream(stream));
   if (rc) return rc;
   QB_CUDA(cudaStreamSynchronize(as_stream(stream)));
   QB_REQUIRE(h == 0, QTIP_E_KERNEL, "a bounded pipeline wait of a tensor-core kernel ran out (status %d)", h);
   QB_REQUIRE(v == 0, QTIP_E_KERNEL, "a bounded wait of the cluster Viterbi kernel ran out (status %d)", v);
+  QB_REQUIRE(na == 0, QTIP_E_KERNEL,
+             "a bounded wait of the cluster Viterbi kernel ran out inside qtip_quantize_tiles_noalloc (status %d)", na);
+  return QTIP_OK;
+}
+extern "C" int qtip_debug_set_status(int which, int value, void* stream) {
+  QB_REQUIRE(which >= 0 && which <= 2, QTIP_E_ARG, "qtip_debug_set_status: which = %d", which);
+  if (which != 0) return viterbi_set_status(which, value, as_stream(stream));
+  void* ft = nullptr;
+  QB_CUDA(cudaGetSymbolAddress(&ft, g_ft_status));
+  QB_CUDA(cudaMemcpyAsync(ft, &value, sizeof value, cudaMemcpyHostToDevice, as_stream(stream)));
+  QB_CUDA(cudaStreamSynchronize(as_stream(stream)));
   return QTIP_OK;
 }

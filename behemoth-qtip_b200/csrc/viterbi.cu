@@ -6,10 +6,7 @@
 //   new minimum of group j = min over d of float((bits(c) & ~15) | d); back-pointer = low 4 bits of that minimum,
 //   stored minimum = the same with the low 4 bits cleared. The last step takes the untagged argmin, lowest state on ties.
 //
-// Two implementations live here:
-//  * vit_fwd_tile_kernel: one CTA per sequence, LUT through a compact shared table, back-pointers in the layout of the
-//    reference's k_viterbi_fwd ([B][127][1024] uint16). Used by the kernel-level entry points.
-//  * vit_fwd_cluster_kernel: the throughput path. An 8-CTA thread-block cluster owns the 65,536 states of the trellis
+// vit_fwd_cluster_kernel: an 8-CTA thread-block cluster owns the 65,536 states of the trellis
 //    (8,192 per SM, one group index j and its 16 predecessors d per thread), keeps each state's LUT pair and norm in
 //    registers for the whole launch, and runs 8 sequences at a time through them. The 4,096 group minima of a step are
 //    exchanged between the 8 SMs through distributed shared memory (each minimum is pushed with st.async to the one CTA
@@ -50,95 +47,7 @@ __device__ __forceinline__ void take_better(float& bv, uint32_t& bs, float ov, u
   if (ov < bv || (ov == bv && os < bs)) bv = ov, bs = os;
 }
 
-// ------------------------------------------------------------------------------------------------- one CTA per sequence
-
-constexpr int kTileThreads = 1024;
-
-__global__ __launch_bounds__(kTileThreads) void vit_fwd_tile_kernel(const float* __restrict__ X,
-                                                                    const int* __restrict__ overlap, int roll,
-                                                                    uint16_t* __restrict__ A,
-                                                                    uint16_t* __restrict__ final_state,
-                                                                    const uint32_t* __restrict__ lut_h2,
-                                                                    uint32_t tag_mask) {
-  __shared__ float M[2][4096];
-  __shared__ float xs[256];
-  __shared__ float tl0[1024], tl1[1024], tnr[1024];  // compact LUT by entry (sign << 9 | index)
-  __shared__ float rv[32];
-  __shared__ uint32_t rs[32];
-  const int b = blockIdx.x, t = threadIdx.x, g = t >> 2;
-  const float* xb = X + size_t(b) * 256;
-  if (t < 256) xs[t] = round_half(roll ? xb[(t + 128) & 255] : xb[t]);
-  // Every state with the same entry holds the same pair, so concurrent writers store identical values.
-  for (uint32_t s = t; s < 65536; s += kTileThreads) {
-    const uint32_t u = lut_h2[s], e = lut_entry(s);
-    const float a = half_lo(u), c = half_hi(u);
-    tl0[e] = a;
-    tl1[e] = c;
-    tnr[e] = __fadd_rn(__fmul_rn(a, a), __fmul_rn(c, c));
-  }
-  const int ov = overlap ? overlap[b] : -1;
-  for (int k = t; k < 4096; k += kTileThreads) M[0][k] = (ov < 0 || k == ov) ? 0.f : 1e30f;
-  __syncthreads();
-
-  uint16_t* Ab = A + size_t(b) * 127 * 1024;
-  int cur = 0;
-  for (int i = 0; i < 127; ++i) {
-    const float x0 = xs[2 * i], x1 = xs[2 * i + 1];
-    const float m0 = round_half(-2.f * x0), m1 = round_half(-2.f * x1);
-    const float xx = __fadd_rn(__fmul_rn(x0, x0), __fmul_rn(x1, x1));
-    float best[4] = {3e30f, 3e30f, 3e30f, 3e30f};
-#pragma unroll 4
-    for (int d = 0; d < 16; ++d) {
-      const float mp = __fadd_rn(M[cur][(d << 8) | g], xx);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint32_t e = lut_entry(uint32_t((d << 12) | (t << 2) | q));
-        const float c = state_cost(tl0[e], tl1[e], tnr[e], mp, m0, m1);
-        best[q] = fminf(best[q], tag_cost(c, tag_mask, d));
-      }
-    }
-    uint32_t pk = 0;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const uint32_t bb = __float_as_uint(best[q]);
-      pk |= (bb & 15u) << (4 * q);
-      M[cur ^ 1][(t << 2) | q] = __uint_as_float(bb & ~15u);
-    }
-    Ab[i * 1024 + t] = uint16_t(pk);
-    __syncthreads();
-    cur ^= 1;
-  }
-  {
-    const float x0 = xs[254], x1 = xs[255];
-    const float m0 = round_half(-2.f * x0), m1 = round_half(-2.f * x1);
-    const float xx = __fadd_rn(__fmul_rn(x0, x0), __fmul_rn(x1, x1));
-    float bv = 3e30f;
-    uint32_t bs = 0xffffffffu;
-    for (int d = 0; d < 16; ++d) {
-      const float mp = __fadd_rn(M[cur][(d << 8) | g], xx);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int j = (t << 2) | q;
-        if (ov >= 0 && j != ov) continue;
-        const uint32_t s = (uint32_t(d) << 12) | uint32_t(j);
-        const uint32_t e = lut_entry(s);
-        take_better(bv, bs, state_cost(tl0[e], tl1[e], tnr[e], mp, m0, m1), s);
-      }
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1)
-      take_better(bv, bs, __shfl_xor_sync(0xffffffffu, bv, off), __shfl_xor_sync(0xffffffffu, bs, off));
-    if ((t & 31) == 0) rv[t >> 5] = bv, rs[t >> 5] = bs;
-    __syncthreads();
-    if (t < 32) {
-      bv = rv[t], bs = rs[t];
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1)
-        take_better(bv, bs, __shfl_xor_sync(0xffffffffu, bv, off), __shfl_xor_sync(0xffffffffu, bs, off));
-      if (t == 0) final_state[b] = uint16_t(bs);
-    }
-  }
-}
+// ------------------------------------------------------------------------------------------------- backtraces
 
 // Back-pointer lookup in the [127][1024] uint16 layout.
 __device__ __forceinline__ uint32_t prev_state_u16(const uint16_t* Ab, int i, uint32_t s) {
@@ -523,8 +432,52 @@ __global__ void vit_finish_w_kernel(const uint32_t* __restrict__ bp, const uint1
 // ------------------------------------------------------------------------------------------------- host side
 
 __device__ int g_vit_status;  // time-outs of cluster launches made through the kernel-level entry point
-int viterbi_read_status(int* value, cudaStream_t s) {
-  QB_CUDA(cudaMemcpyFromSymbolAsync(value, g_vit_status, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
+
+// ---- scratch of the allocation-free entry point (qtip_quantize_tiles_noalloc, at the end of this file)
+constexpr int kNoAllocMaxTiles = 64;
+constexpr size_t kNoAllocHeader = 256;  // status word; the same header a caller-owned workspace starts with
+constexpr size_t kNoAllocBytes = kNoAllocHeader + 256 + 256 + size_t(kNoAllocMaxTiles) * 16 * 4096 * 4;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+static std::mutex g_noalloc_mu;
+static void* g_noalloc_ptr[64];  // device address of the array on each device, resolved on first use
+
+// Status words that live inside the library (no caller-owned workspace to carry them): the kernel-level cluster
+// launches and the built-in scratch of the allocation-free entry point. Queues the copies on `s` and, behind them,
+// the clearing of both words, so that one reported time-out does not stay set for the rest of the process.
+int viterbi_read_status(int* kernel_level, int* noalloc, cudaStream_t s) {
+  *kernel_level = 0, *noalloc = 0;
+  void* kv = nullptr;
+  QB_CUDA(cudaGetSymbolAddress(&kv, g_vit_status));
+  QB_CUDA(cudaMemcpyAsync(kernel_level, kv, sizeof(int), cudaMemcpyDeviceToHost, s));
+  QB_CUDA(cudaMemsetAsync(kv, 0, sizeof(int), s));
+  int dev = -1;
+  QB_CUDA(cudaGetDevice(&dev));
+  void* na = nullptr;
+  if (dev >= 0 && dev < 64) {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    na = g_noalloc_ptr[dev];
+  }
+  if (na) {  // the entry point has run on this device
+    QB_CUDA(cudaMemcpyAsync(noalloc, na, sizeof(int), cudaMemcpyDeviceToHost, s));
+    QB_CUDA(cudaMemsetAsync(na, 0, sizeof(int), s));
+  }
+  return QTIP_OK;
+}
+
+int viterbi_set_status(int which, int value, cudaStream_t s) {
+  void* at = nullptr;
+  if (which == 1) {
+    QB_CUDA(cudaGetSymbolAddress(&at, g_vit_status));
+  } else {
+    int dev = -1;
+    QB_CUDA(cudaGetDevice(&dev));
+    QB_REQUIRE(dev >= 0 && dev < 64, QTIP_E_DEVICE, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    at = g_noalloc_ptr[dev];
+    QB_REQUIRE(at, QTIP_E_ARG, "qtip_quantize_tiles_noalloc has not run on device %d yet", dev);
+  }
+  QB_CUDA(cudaMemcpyAsync(at, &value, sizeof(int), cudaMemcpyHostToDevice, s));
+  QB_CUDA(cudaStreamSynchronize(s));  // `value` is on this function's stack
   return QTIP_OK;
 }
 
@@ -641,28 +594,34 @@ int quantize_tiles_impl(const float* X, int B, int b0, const uint32_t* lut, uint
     QB_CUDA(cudaStreamWaitEvent(ls->side, ls->fork, 0));
   }
   const int cap = two_lanes ? half : w.cap;
-  int lane = 0;
-  for (int c0 = 0; c0 < B; c0 += cap, lane ^= 1) {
-    const int nb = B - c0 < cap ? B - c0 : cap;
-    const float* xc = X + size_t(c0) * 256;
-    const int o = (two_lanes && lane) ? half : 0;  // this lane's part of the scratch arrays
-    cudaStream_t st = (two_lanes && lane) ? ls->side : s;
-    uint32_t* bp = w.bp + size_t(o) * (kBpBytes / 4);
-    int rc = launch_cluster_fwd(info, xc, nullptr, 1, nb, bp, 8, w.fs + o, lut, w.status, st);
-    if (rc) return rc;
-    vit_overlap_w_kernel<<<blocks_for(nb, 64), 64, 0, st>>>(bp, w.fs + o, nb, w.ov + o);
-    QB_LAUNCHED();
-    rc = launch_cluster_fwd(info, xc, w.ov + o, 0, nb, bp, 0, w.fs + o, lut, w.status, st);
-    if (rc) return rc;
-    vit_finish_w_kernel<<<blocks_for(nb, 64), 64, 0, st>>>(bp, w.fs + o, nb, b0 + c0, Q, nblk, blk,
-                                                           hat ? hat + size_t(c0) * 256 : nullptr, hatWT, m, col0, lut);
-    QB_LAUNCHED();
-  }
+  // The chunk loop as a function, so that every way out of it passes the join below: a failed launch must not leave the
+  // side stream un-joined (it may still be writing the outputs, and an open fork would invalidate a stream capture).
+  auto chunks = [&]() -> int {
+    int lane = 0;
+    for (int c0 = 0; c0 < B; c0 += cap, lane ^= 1) {
+      const int nb = B - c0 < cap ? B - c0 : cap;
+      const float* xc = X + size_t(c0) * 256;
+      const int o = (two_lanes && lane) ? half : 0;  // this lane's part of the scratch arrays
+      cudaStream_t st = (two_lanes && lane) ? ls->side : s;
+      uint32_t* bp = w.bp + size_t(o) * (kBpBytes / 4);
+      int rc = launch_cluster_fwd(info, xc, nullptr, 1, nb, bp, 8, w.fs + o, lut, w.status, st);
+      if (rc) return rc;
+      vit_overlap_w_kernel<<<blocks_for(nb, 64), 64, 0, st>>>(bp, w.fs + o, nb, w.ov + o);
+      QB_LAUNCHED();
+      rc = launch_cluster_fwd(info, xc, w.ov + o, 0, nb, bp, 0, w.fs + o, lut, w.status, st);
+      if (rc) return rc;
+      vit_finish_w_kernel<<<blocks_for(nb, 64), 64, 0, st>>>(bp, w.fs + o, nb, b0 + c0, Q, nblk, blk,
+                                                             hat ? hat + size_t(c0) * 256 : nullptr, hatWT, m, col0, lut);
+      QB_LAUNCHED();
+    }
+    return QTIP_OK;
+  };
+  const int rc = chunks();
   if (two_lanes) {
     QB_CUDA(cudaEventRecord(ls->join, ls->side));
     QB_CUDA(cudaStreamWaitEvent(s, ls->join, 0));
   }
-  return QTIP_OK;
+  return rc;
 }
 
 }  // namespace qb
@@ -681,16 +640,6 @@ extern "C" int qtip_k_viterbi_fwd(const float* X_d, const int* overlap_d, int ro
   QB_CUDA(cudaGetSymbolAddress(&st, g_vit_status));
   return launch_cluster_fwd<true>(info, X_d, overlap_d, roll, B, reinterpret_cast<uint32_t*>(A_d), 0, final_state_d,
                                   lut_h2_d, static_cast<int*>(st), as_stream(stream));
-}
-// The one-CTA-per-sequence kernel behind the same arguments (kept as a simple second implementation for tests).
-extern "C" int qtip_k_viterbi_fwd_simple(const float* X_d, const int* overlap_d, int roll, int B, uint16_t* A_d,
-                                         uint16_t* final_state_d, const uint32_t* lut_h2_d, void* stream) {
-  QB_REQUIRE(X_d && A_d && final_state_d && lut_h2_d && B >= 0, QTIP_E_ARG, "qtip_k_viterbi_fwd_simple: bad argument");
-  if (B == 0) return QTIP_OK;
-  vit_fwd_tile_kernel<<<unsigned(B), kTileThreads, 0, as_stream(stream)>>>(X_d, overlap_d, roll, A_d, final_state_d,
-                                                                          lut_h2_d, kTagMask);
-  QB_LAUNCHED();
-  return QTIP_OK;
 }
 extern "C" int qtip_k_viterbi_overlap(const uint16_t* A_d, const uint16_t* final_state_d, int B, int* overlap_d,
                                       void* stream) {
@@ -778,11 +727,8 @@ extern "C" int qtip_quantize_tiles_scatter(const float* X_d, int B, int b0, cons
 // cudaMalloc is banned because it synchronises the whole device and can fail once memory is fragmented. For them the
 // Viterbi scratch (status word, final states, overlaps, back-pointer words) lives in the array below, which is part of
 // the loaded module: every GPU that loads the library holds these 16 MiB until the process exits.
-constexpr int kNoAllocMaxTiles = 64;
-constexpr size_t kNoAllocBytes = kWsHeader + 256 + 256 + size_t(kNoAllocMaxTiles) * kBpBytes;
-static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
-static std::mutex g_noalloc_mu;
-static void* g_noalloc_ptr[64];  // device address of the array on each device, resolved on first use
+static_assert(kNoAllocHeader == kWsHeader && kNoAllocBytes == kWsHeader + 256 + 256 + size_t(kNoAllocMaxTiles) * kBpBytes,
+              "the built-in scratch is laid out like a workspace of 64 sequences");
 
 extern "C" int qtip_quantize_tiles_noalloc(const float* X_d, int B, const uint32_t* lut_h2_d, uint16_t* states_d,
                                            float* hat_d, void* stream) {
@@ -794,6 +740,7 @@ extern "C" int qtip_quantize_tiles_noalloc(const float* X_d, int B, const uint32
   if (!device_info()) return QTIP_E_DEVICE;
   int dev = 0;
   QB_CUDA(cudaGetDevice(&dev));
+  QB_REQUIRE(dev >= 0 && dev < 64, QTIP_E_DEVICE, "device index %d out of range", dev);
   void* scratch = nullptr;
   {
     std::lock_guard<std::mutex> lk(g_noalloc_mu);
@@ -805,9 +752,10 @@ extern "C" int qtip_quantize_tiles_noalloc(const float* X_d, int B, const uint32
     }
     scratch = g_noalloc_ptr[dev];
   }
-  // The array keeps whatever the previous call left: the status word is cleared by the shared body (reset_status),
-  // every other field is written before it is read.
-  return quantize_tiles_impl(X_d, B, 0, lut_h2_d, states_d, 1, 0, hat_d, nullptr, 0, 0, scratch, kNoAllocBytes, true,
+  // The array keeps whatever the previous call left. Every field but the status word is written before it is read; the
+  // status word is NOT cleared here, so that a time-out of any call since the last qtip_kernel_status (which reads and
+  // clears it) is still reported.
+  return quantize_tiles_impl(X_d, B, 0, lut_h2_d, states_d, 1, 0, hat_d, nullptr, 0, 0, scratch, kNoAllocBytes, false,
                              as_stream(stream), false);  // one lane: this entry point creates no streams or events
 }
 

@@ -26,7 +26,7 @@ sys.path.insert(0, ROOT)
 M, N_COLS = 12288, 12288
 LANE_OPS_PER_WEIGHT = 327680  # 2 passes x 128 steps x 65,536 states / 256 weights x 5 ops (add, 2 fma, tag, min)
 METRIC = "viterbi_quantized_weights_per_second"
-NCU_DRAM_BYTES_PER_TILE_PASS = 9104128 // 240  # dram read + write of one 240-sequence launch (profiles/)
+NCU_DRAM_BYTES_PER_TILE_PASS = 9104128 // 240  # DRAM read + write of one profiled 240-sequence launch
 
 
 def measured_peaks():
@@ -227,13 +227,21 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=M, help="rows of the matrix (default: the full 12288)")
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMV section and the CPU baseline")
-    ap.add_argument("--workload", default="viterbi", choices=["viterbi", "ldlq", "layer"],
+    ap.add_argument("--workload", default="viterbi", choices=["viterbi", "ldlq", "layer", "kernel"],
                     help="viterbi: the headline identity-Hessian encode; ldlq: LDLQ + Viterbi on a 12288 x 28672 matrix "
-                         "with a synthetic correlated Hessian (secondary line)")
+                         "with a synthetic correlated Hessian (secondary line); layer: the products of one layer; "
+                         "kernel: a few launches of one kernel on a small case (for profiler captures)")
     ap.add_argument("--ldlq-shape", default="12288x28672", help="m x n of the ldlq workload")
+    ap.add_argument("--kernel", default="gemv", choices=["viterbi", "gemv", "fused", "prefill"],
+                    help="--workload kernel: which kernel")
+    ap.add_argument("--size", type=int, default=16384, help="--workload kernel: sequences (viterbi) or output rows")
+    ap.add_argument("--tokens", type=int, default=0, help="--workload kernel: token count (fused: 64, prefill: 2048)")
+    ap.add_argument("--splits", type=int, default=1, help="--workload kernel: K-splits (fused, gemv)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.workload == "kernel":
+        return kernel_workload(args)
     if args.workload == "ldlq":
         return ldlq_workload(args)
     if args.workload == "layer" and int(os.environ.get("WORLD_SIZE", "1")) > 1:
@@ -730,6 +738,67 @@ def layer_workload(args):
     print(json.dumps({"metric": "qtip_layer_products", "unit": "us per layer", "n_gpus": 1, "data": "synthetic",
                       "config": {"workload": "mistral_large_layer_products", "hidden": hidden, "intermediate": inter,
                                  "code_bytes": code_bytes, "weights": weights, "peaks": peak_src}, "tokens": out}))
+
+
+def kernel_workload(args):
+    """A few launches of one kernel of the path on a small fixed case, timed with CUDA events: the command a profiler
+    capture wraps (one kernel, few launches before it, a few hundred MB on the device at most).
+        --kernel viterbi --size <sequences>                          forward pass of the cluster Viterbi kernel
+        --kernel gemv    --size <out rows> [--splits s]              qtip_multiply, one token, <out rows> x 12288
+        --kernel fused   --size <out rows> [--tokens t] [--splits s] qtip_multiply_tc
+        --kernel prefill --size <out rows> [--tokens t]              qtip_prefill_gemm on a dense bf16 matrix"""
+    import torch
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    codec, linear, synth = pkg.codec, pkg.linear, pkg.synth
+    torch.cuda.set_device(0)
+    codec.init()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(9)
+    size, n_in = args.size, 12288
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def qtip_linear(n_out):
+        trellis = torch.randint(-32768, 32768, ((n_out // 16) * (n_in // 16) * 32,), generator=gen, device="cuda",
+                                dtype=torch.int16)
+        su, sv = torch.from_numpy(synth.signs(n_in, 7)).cuda(), torch.from_numpy(synth.signs(n_out, 8)).cuda()
+        return linear.Matrix(trellis, su, sv, linear.runtime_lut(synth.seeded_tlut(1)), n_in, n_out)
+
+    if args.kernel == "viterbi":
+        lut_d, _ = codec.device_lut(synth.seeded_tlut(1))
+        X = torch.randn(size, 256, generator=gen, device="cuda")
+        bp = torch.empty((size, 16, 4096), dtype=torch.int32, device="cuda")
+        fs = torch.empty(size, dtype=torch.int16, device="cuda")
+        fn = lambda: codec.k_viterbi_fwd_words(X, None, 1, size, bp, 0, fs, lut_d, status)  # noqa: E731
+    elif args.kernel == "prefill":
+        tokens = args.tokens or 2048
+        wd = torch.randn(size, n_in, generator=gen, device="cuda").to(torch.bfloat16)
+        x = torch.randn(tokens, n_in, generator=gen, device="cuda").to(torch.bfloat16)
+        z = torch.empty((tokens, size), dtype=torch.float32, device="cuda")
+        fn = lambda: linear.prefill_gemm(wd, x, z, size, n_in, size, tokens, status)  # noqa: E731
+    elif args.kernel == "fused":
+        tokens = args.tokens or 64
+        w = qtip_linear(size)
+        x = torch.randn(tokens, n_in, generator=gen, device="cuda").to(torch.bfloat16)
+        z = torch.empty((args.splits, tokens, size), dtype=torch.float32, device="cuda")
+        fn = lambda: linear.qtip_multiply_tc(w, x, z, size, args.splits, tokens, status)  # noqa: E731
+    else:
+        w = qtip_linear(size)
+        rot = torch.randn(n_in, generator=gen, device="cuda").to(torch.bfloat16)
+        z = torch.empty((args.splits, size), dtype=torch.float32, device="cuda")
+        fn = lambda: linear.qtip_multiply(w, rot, z, size, args.splits, 1)  # noqa: E731
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    assert int(status) == 0, "a bounded wait ran out"
+    linear.kernel_status()
+    print(json.dumps({"workload": "kernel", "kernel": args.kernel, "size": size, "tokens": args.tokens,
+                      "splits": args.splits, "us_per_launch": e0.elapsed_time(e1) * 1e3 / 3}))
 
 
 def _time_us(fn, iters, torch):

@@ -61,10 +61,6 @@ int qtip_k_ldlq_prep(const float* WT_d, const float* hatWT_d, const float* prod_
  * NULL, roll = 1 reads X rolled by 128. src/viterbi.hip:49-188,275-279 (k_viterbi_fwd). */
 int qtip_k_viterbi_fwd(const float* X_d, const int* overlap_d, int roll, int B, uint16_t* A_d,
                        uint16_t* final_state_d, const uint32_t* lut_h2_d, void* stream);
-/* Same arguments and results, computed by a plain one-CTA-per-sequence kernel (a second, independent implementation kept
- * for cross-checks; several times slower). */
-int qtip_k_viterbi_fwd_simple(const float* X_d, const int* overlap_d, int roll, int B, uint16_t* A_d,
-                              uint16_t* final_state_d, const uint32_t* lut_h2_d, void* stream);
 /* Pass-1 backtrace: overlap[b] = state(step 64) >> 4. src/viterbi.hip:197-205,280-283 (k_viterbi_overlap). */
 int qtip_k_viterbi_overlap(const uint16_t* A_d, const uint16_t* final_state_d, int B, int* overlap_d, void* stream);
 /* Pass-2 backtrace: states into Q_d[(b0+b)*nblk+blk][128] (may be NULL) and decoded values scattered into
@@ -118,7 +114,9 @@ int qtip_quantize_tiles_scatter(const float* X_d, int B, int b0, const uint32_t*
  * bit-identical to qtip_quantize_tiles. The first call on a device looks the array's device address up
  * (cudaGetSymbolAddress): make that first call outside any stream capture, with the device current. All calls on a
  * device share the one array, so two calls whose kernels can overlap on the GPU (different streams) race; calls on
- * one stream are safe. This entry point has no counterpart in the reference. */
+ * one stream are safe. A hand-shake between thread blocks that timed out (outputs then invalid) is reported by
+ * qtip_kernel_status(), which reads and clears the status word kept in the array; the call itself does not clear it.
+ * This entry point has no counterpart in the reference. */
 int qtip_quantize_tiles_noalloc(const float* X_d, int B, const uint32_t* lut_h2_d, uint16_t* states_d, float* hat_d,
                                 void* stream);
 
@@ -250,8 +248,14 @@ int qtip_prefill_gemm_splitk(const uint16_t* w_dense_d, const uint16_t* x_d, flo
 int qtip_multiply_tc(qtip_matrix w, const uint16_t* rotated_d, float* z_d, int stride, int splits, int tokens,
                      int* status_d, void* stream);
 /* Synchronises `stream`; QTIP_E_KERNEL if a kernel launched through an entry point without a status argument
- * (qtip_multiply_batch's tensor-core path, qtip_k_viterbi_fwd) reported a bounded wait that ran out. */
+ * (qtip_multiply_batch's tensor-core path, qtip_k_viterbi_fwd, qtip_quantize_tiles_noalloc) reported a bounded wait
+ * that ran out since the last call. The status words live inside the library, one set per device; this call reads
+ * them on the current device and clears them (clear on read), so an error is reported once. */
 int qtip_kernel_status(void* stream);
+/* Test hook: stores `value` into one of those status words on the current device (which: 0 = tensor-core kernels,
+ * 1 = kernel-level cluster Viterbi, 2 = built-in scratch of qtip_quantize_tiles_noalloc; the last needs one earlier
+ * call of that entry point on the device). Lets a test drive the reporting path without making any kernel wait. */
+int qtip_debug_set_status(int which, int value, void* stream);
 
 /* FP8 (e4m3) W8A16 projection of the K/V weights kept beside the QTIP linears: y[t][o] = bf16((sum_i fp8(w[o][i]) *
  * bf16(x[t][i])) * scale[o]), fp32 accumulation. w_d [out][in] bytes, scale_d [out], x_d [tokens][in] bf16, y_d

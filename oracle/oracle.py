@@ -20,14 +20,28 @@ _i8p = np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS")
 _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 
 
+def reference_root():
+    """Root of the reference project's source tree: the QTIP_REFERENCE_ROOT environment variable, else the Makefile's
+    default (REF). The tree is optional: without it only the prebuilt files under _ref/ are used."""
+    root = os.environ.get("QTIP_REFERENCE_ROOT")
+    if root:
+        return root
+    with open(os.path.join(_HERE, "Makefile")) as f:
+        for line in f:
+            if line.startswith("REF ?="):
+                return line.split("=", 1)[1].strip()
+    return ""
+
+
 def build(ref=False):
     """Compile the oracle (and, with ref=True and the reference tree present, the reference's CPU code and, when nvcc is
     there, the reference's CUDA kernels for this path)."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
-    if ref and os.path.isdir("/root/reference/src"):
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref"], stderr=subprocess.DEVNULL)
-        if os.path.exists("/usr/local/cuda/bin/nvcc"):
-            subprocess.check_call(["make", "-s", "-C", _HERE, "refgpu"], stderr=subprocess.DEVNULL)
+    root = reference_root()
+    if ref and root and os.path.isdir(os.path.join(root, "src")):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "REF=" + root], stderr=subprocess.DEVNULL)
+        if os.path.exists(os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")):
+            subprocess.check_call(["make", "-s", "-C", _HERE, "refgpu", "REF=" + root], stderr=subprocess.DEVNULL)
 
 
 def _load(path):

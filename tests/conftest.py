@@ -8,7 +8,15 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 GOLDEN = os.path.join(ROOT, "tests", "golden")
-REFVEC = "/root/reference/tests/refvec"
+
+
+def _reference_root():
+    from oracle.oracle import reference_root
+    return reference_root()
+
+
+REFERENCE_ROOT = _reference_root()  # QTIP_REFERENCE_ROOT, else the default of oracle/Makefile; may not exist
+REFVEC = os.path.join(REFERENCE_ROOT, "tests", "refvec")
 
 
 def pytest_configure(config):
@@ -46,6 +54,17 @@ def gpu(pkg):
     torch.cuda.set_device(0)
     pkg.codec.init()
     return pkg
+
+
+@pytest.fixture(scope="session")
+def refgpu(gpu):
+    """The reference's own CUDA kernels for this path, compiled in place for sm_100a; skips when not prebuilt."""
+    from oracle.oracle import ReferenceGpu
+    r = ReferenceGpu()
+    if not r.available:
+        pytest.skip("the reference's CUDA kernels are not built (make -C oracle refgpu)")
+    r.initialize_tables()
+    return r
 
 
 def golden(name):

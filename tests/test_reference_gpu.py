@@ -11,16 +11,6 @@ from test_viterbi_gpu import dev, gpu_lut, u16
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def refgpu(gpu):
-    from oracle.oracle import ReferenceGpu
-    r = ReferenceGpu()
-    if not r.available:
-        pytest.skip("the reference's CUDA kernels are not built (make -C oracle refgpu)")
-    r.initialize_tables()
-    return r
-
-
 def p(t):
     return None if t is None else t.data_ptr()
 

@@ -183,23 +183,21 @@ def test_invariants_at_scale(gpu):
 
 
 @pytest.mark.parametrize("B", [1, 13, 64])
-def test_kernel_level_forward_two_implementations_agree(gpu, hyb, B):
-    """qtip_k_viterbi_fwd (cluster kernel writing the reference's back-pointer layout) against the plain
-    one-CTA-per-sequence kernel: every back-pointer word and final state, both passes, ragged batch sizes."""
-    tl, _, _ = hyb
+def test_kernel_level_forward_ragged_batches_bit_exact(gpu, oracle, hyb, B):
+    """qtip_k_viterbi_fwd (cluster kernel writing the reference's back-pointer layout) against the oracle's restatement
+    of the reference kernel: every back-pointer word and final state, both passes, batch sizes that leave the last
+    cluster batch partly filled."""
+    tl, lut, _ = hyb
     lut_d, _ = gpu_lut(gpu, tl)
-    X = dev((np.random.default_rng(100 + B).standard_normal((B, 256)) * 1.1).astype(np.float32))
-    c = gpu.codec
-    A, A2 = (torch.zeros((B, 127, 1024), dtype=torch.int16, device="cuda") for _ in range(2))
-    fs, fs2 = (torch.zeros(B, dtype=torch.int16, device="cuda") for _ in range(2))
-    ov = torch.empty(B, dtype=torch.int32, device="cuda")
-    c.k_viterbi_fwd(X, None, 1, B, A, fs, lut_d)
-    c.k_viterbi_fwd_simple(X, None, 1, B, A2, fs2, lut_d)
-    assert torch.equal(A, A2) and torch.equal(fs, fs2)
-    c.k_viterbi_overlap(A, fs, B, ov)
-    c.k_viterbi_fwd(X, ov, 0, B, A, fs, lut_d)
-    c.k_viterbi_fwd_simple(X, ov, 0, B, A2, fs2, lut_d)
-    assert torch.equal(A, A2) and torch.equal(fs, fs2)
+    X = (np.random.default_rng(100 + B).standard_normal((B, 256)) * 1.1).astype(np.float32)
+    A1, fs1, ov, A2, fs2, Q = staged(gpu, X, lut_d)
+    oA1, ofs1 = oracle.viterbi_fwd(X, None, 1, lut)
+    assert np.array_equal(A1, oA1) and np.array_equal(fs1, ofs1)
+    oov = oracle.viterbi_overlap(oA1, ofs1)
+    assert np.array_equal(ov, oov)
+    oA2, ofs2 = oracle.viterbi_fwd(X, oov, 0, lut)
+    assert np.array_equal(A2, oA2) and np.array_equal(fs2, ofs2)
+    assert np.array_equal(Q, oracle.viterbi_finish(oA2, ofs2, lut))
     gpu.linear.kernel_status()
 
 
