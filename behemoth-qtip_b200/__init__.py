@@ -4,5 +4,6 @@
 runtime's QTIP linear operator (QtipMatrix, qtip_prepare / qtip_multiply / qtip_finish / qtip_forward, ...).
 PyTorch is used only for device memory, streams and torch.distributed.
 """
-from ._lib import LIB_PATH, Library, QtipError, QtipMatrix, QtipTpExchange, exported_names, lib  # noqa: F401
-from . import codec, linear, sharding, synth, tp  # noqa: F401
+from ._lib import (LIB_PATH, Library, QtipCheckpointLinear, QtipError, QtipGroupLinear, QtipMatrix,  # noqa: F401
+                   QtipTpExchange, exported_names, lib)
+from . import checkpoint, codec, linear, sharding, synth, tp  # noqa: F401

@@ -27,6 +27,18 @@ class QtipTpExchange(C.Structure):
     _fields_ = [("base", C.c_void_p * 8), ("bytes", C.c_size_t), ("rank", C.c_int), ("ranks", C.c_int)]
 
 
+class QtipCheckpointLinear(C.Structure):
+    """POD mirror of qtip_checkpoint_linear: host pointers of one linear's checkpoint tensors."""
+    _fields_ = [("name", C.c_char_p), ("m", C.c_int), ("n", C.c_int), ("trellis_h", C.c_void_p),
+                ("su_bf16_h", C.c_void_p), ("sv_h", C.c_void_p), ("tlut_h", C.c_void_p)]
+
+
+class QtipGroupLinear(C.Structure):
+    """POD mirror of qtip_group_linear: one linear of a Hessian group (inputs W_d, m, sv_d, trellis_d; the rest is output)."""
+    _fields_ = [("W_d", C.c_void_p), ("m", C.c_long), ("sv_d", C.c_void_p), ("trellis_d", C.c_void_p),
+                ("wscale", C.c_float), ("proxy", C.c_double), ("proxy_rot_reg", C.c_double)]
+
+
 _P, _I, _L, _Z, _F = C.c_void_p, C.c_int, C.c_long, C.c_size_t, C.c_float
 _X = C.POINTER(QtipTpExchange)
 
@@ -62,7 +74,13 @@ SIGNATURES = {
     "qtip_ldlq": [_P, _P, _L, _L, _L, _L, _P, _P, _P, _P, _Z, _P],
     "qtip_quantize_linear": [_P, _P, _L, _L, _P, _P, _P, C.c_double, C.c_double, _P, _P, _P, _P, C.POINTER(C.c_float), _P,
                              _Z, _P],
+    "qtip_quantize_group": [C.POINTER(QtipGroupLinear), _I, _L, _P, _P, _P, C.c_double, _P, C.c_double, C.c_double, _P, _P,
+                            _P, _P, _Z, _P],
     "qtip_rotate_hessian": [_P, _L, _P, C.c_double, _P, C.POINTER(C.c_double), _P, _P],
+    "qtip_block_ldl": [_P, _L, _P, _P, _P, _Z, _P],
+    "qtip_block_ldl_status": [_P, _P],
+    "qtip_write_layer_file": [C.c_char_p, _I, C.POINTER(QtipCheckpointLinear), _I],
+    "qtip_read_layer_linear": [C.c_char_p, _I, C.c_char_p, _I, _I, _P, _P, _P, _P],
     "qtip_pack_trellis": [_P, _L, _P, _P],
     "qtip_unpack_trellis": [_P, _L, _P, _P],
     "qtip_swizzle_for_kernel": [_P, _I, _I, _P, _P],
@@ -99,6 +117,8 @@ _RESTYPES = {
     "qtip_abi_version": (C.c_int, []),
     "qtip_quantize_workspace_bytes": (C.c_size_t, [_I]),
     "qtip_ldlq_workspace_bytes": (C.c_size_t, [_L, _L]),
+    "qtip_block_ldl_workspace_bytes": (C.c_size_t, [_L]),
+    "qtip_quantize_group_workspace_bytes": (C.c_size_t, [_L, _L, _L]),
     "qtip_quantize_linear_workspace_bytes": (C.c_size_t, [_L, _L]),
     "qtip_tp_exchange_bytes": (C.c_size_t, [_I, _I, _I]),
 }

@@ -5,7 +5,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["tables.cu", "viterbi.cu", "ldlq.cu", "hadamard.cu", "elementwise.cu", "decode.cu", "fp8.cu", "gemm_tc.cu",
-           "trellis_tc.cu"]
+           "trellis_tc.cu", "block_ldl.cu", "group.cu", "checkpoint.cpp"]
 LIB = os.path.join(HERE, "libqtip_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 EXTRA = os.environ.get("QTIP_NVCC_FLAGS", "").split()
@@ -30,7 +30,7 @@ def build(force=False, verbose=False):
     os.makedirs(obj_dir, exist_ok=True)
     procs = []
     for src in SOURCES:
-        obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
+        obj = os.path.join(obj_dir, os.path.splitext(src)[0] + ".o")
         cmd = [NVCC, *FLAGS, *EXTRA, "-c", os.path.join(HERE, "csrc", src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")

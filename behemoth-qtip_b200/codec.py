@@ -357,6 +357,53 @@ def quantize_linear_fused(W, L, su, sv, lut_h2, lut_rms, workspace=None, scale_o
             "hatWT": hatWT, "Q": Q, "workspace": workspace}
 
 
+def block_ldl(HR, want_f64=False, workspace=None):
+    """ldl_hessian of the reference (src/quantizer.cpp:154-165) on the GPU: fp64 symmetrisation, blocked Cholesky and the
+    16 x 16 block LDL of HR [n, n] f32 (the rotated, damped Hessian). Returns L [n, n] f32, strictly block-lower (with
+    want_f64 also the values before rounding to fp32). Raises QtipError (code -6) when HR is not positive definite."""
+    init()
+    n = HR.shape[0]
+    if workspace is None:
+        workspace = Workspace(lib().raw("qtip_block_ldl_workspace_bytes")(int(n)))
+    L = torch.empty((n, n), dtype=torch.float32, device=HR.device)
+    L64 = torch.empty((n, n), dtype=torch.float64, device=HR.device) if want_f64 else None
+    lib().call("qtip_block_ldl", _p(HR, torch.float32), n, _p(L, torch.float32), _p(L64, torch.float64), workspace.ptr,
+               workspace.nbytes, _stream())
+    lib().call("qtip_block_ldl_status", workspace.ptr, _stream())
+    return (L, L64) if want_f64 else L
+
+
+def quantize_group(weights, HR, L, su, svs, creg, lut_h2, lut_rms, scale_override=0.9, workspace=None):
+    """quantize_group of the reference (src/quantizer.cpp:166-346) as ONE C-ABI call: `weights` [m_i, n] f32 device
+    tensors (overwritten) that share the rotated Hessian HR, its block LDL factor L and SU; `svs` their sign vectors.
+    Returns one dict per linear (trellis in kernel layout, SU bf16, SV = sign * Wscale, wscale, proxy, proxy_rot_reg)
+    and the shared tensors (WT, hatWT, Q)."""
+    from ._lib import QtipGroupLinear
+    init()
+    n = HR.shape[0]
+    mt = sum(int(w.shape[0]) for w in weights)
+    m_max = max(int(w.shape[0]) for w in weights)
+    dev = HR.device
+    WT = torch.empty((n, mt), dtype=torch.float32, device=dev)
+    hatWT = torch.empty_like(WT)
+    Q = torch.empty(((mt // 16) * (n // 16), 128), dtype=torch.int16, device=dev)
+    trellis = [torch.empty(((w.shape[0] // 16) * (n // 16), 32), dtype=torch.int16, device=dev) for w in weights]
+    lins = (QtipGroupLinear * len(weights))()
+    for i, (w, sv) in enumerate(zip(weights, svs)):
+        assert w.dtype == torch.float32 and w.is_contiguous() and w.shape[1] == n
+        lins[i].W_d, lins[i].m, lins[i].sv_d, lins[i].trellis_d = w.data_ptr(), w.shape[0], sv.data_ptr(), trellis[i].data_ptr()
+    if workspace is None:
+        workspace = Workspace(lib().raw("qtip_quantize_group_workspace_bytes")(n, mt, m_max))
+    lib().call("qtip_quantize_group", lins, len(weights), n, _p(HR, torch.float32), _p(L, torch.float32),
+               _p(su, torch.float32), float(creg), _p(lut_h2, torch.int32), float(lut_rms), float(scale_override),
+               _p(WT, torch.float32), _p(hatWT, torch.float32), _p(Q, torch.int16), workspace.ptr, workspace.nbytes,
+               _stream())
+    workspace.check()
+    outs = [{"trellis": trellis[i], "SU": su.to(torch.bfloat16), "SV": svs[i] * lins[i].wscale, "wscale": lins[i].wscale,
+             "proxy": lins[i].proxy, "proxy_rot_reg": lins[i].proxy_rot_reg} for i in range(len(weights))]
+    return outs, {"WT": WT, "hatWT": hatWT, "Q": Q}
+
+
 def rotate_hessian_fused(H, su, sigma_reg=1e-2):
     """rotate_hessian as ONE C-ABI call (qtip_rotate_hessian): same result, bit for bit."""
     init()

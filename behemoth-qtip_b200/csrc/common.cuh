@@ -41,6 +41,7 @@ int trellis_tc_device_setup();                // trellis_tc.cu
 // viterbi.cu: status words of the kernel-level cluster launches and of the built-in scratch; read, then cleared, on `s`
 int viterbi_read_status(int* kernel_level, int* noalloc, cudaStream_t s);
 int viterbi_set_status(int which, int value, cudaStream_t s);  // test hook behind qtip_debug_set_status
+int block_ldl_device_setup();                // block_ldl.cu
 int hadamard_device_setup();                 // hadamard.cu: uploads the order-12/20/28 factors
 
 // Order-K Hadamard factor (Paley construction), K in {12, 20, 28}; row-major +-1. Returns false otherwise.

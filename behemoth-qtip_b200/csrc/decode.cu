@@ -31,11 +31,10 @@ int trellis_tc_multiply(qtip_matrix w, const uint16_t* x, float* z, int stride, 
 #define QB_GEMV_THREADS 1024
 #endif
 constexpr int kGemmThreads = QB_GEMV_THREADS;  // 1024 (64 registers per thread) or 512 (128)
-constexpr int kWarpsPerItem = 8;
-constexpr int kItemsPerCta = kGemmThreads / 32 / kWarpsPerItem;  // 4
+constexpr int kMaxItemsPerCta = kGemmThreads / 32 / 8;  // 4 concurrent work items of 8 warps each, or 2 x 16, or 1 x 32
 constexpr int kLutBytes = 1024 * 32 * 4;                         // 128 KiB, 32 copies
 #ifndef QB_GEMV_CHUNK
-#define QB_GEMV_CHUNK 4
+#define QB_GEMV_CHUNK 2
 #endif
 constexpr int kChunk = QB_GEMV_CHUNK;  // blocks per register set; two sets alternate, so up to 2 kChunk loads are in flight per warp
 
@@ -290,9 +289,10 @@ __device__ __forceinline__ void tp_wait_warp(TpControl* ctl, int slot, int ranks
 // z[(split * tokens_total + token) * stride + row]; x: [tokens_total][in] bf16 (the rotated input). One launch covers
 // tokens [t0, t0 + tokens), tokens <= 8 NT: each group of 8 tokens is one MMA column block held in registers. XS (one
 // token): the activations are staged in shared memory in fragment order, one 16-byte read per block and lane.
-// Work items are dealt round-robin to groups of 8 warps (4 per CTA) for as many full rounds as there are; the remainder
-// is done by whole CTAs (32 warps per item) so that the tail of the launch is a quarter of a round long.
-template <int NT, bool XS, bool PUSH>
+// Work items are dealt round-robin to groups of 32 / IPC warps (IPC = 4, 2 or 1 items at a time per CTA; the host
+// picks it for the one-token kernel so that a launch with few items still puts a CTA on every SM) for as many full
+// rounds as there are; the remainder is done by whole CTAs (32 warps per item) so that the tail of the launch is short.
+template <int NT, bool XS, bool PUSH, int IPC>
 __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matrix w, const uint16_t* __restrict__ x,
                                                                        float* __restrict__ z, int stride, int splits,
                                                                        int tokens_total, int t0, int tokens,
@@ -331,11 +331,12 @@ __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matr
   c.n2 = w.in / 32, c.in_words = w.in / 2, c.stride = stride, c.splits = splits;
   c.tokens_total = tokens_total, c.t0 = t0, c.tokens = tokens;
   const int n_items = (w.out / 32) * splits;
-  const int slots = gridDim.x * kItemsPerCta;
+  constexpr int ipc = IPC, wpi = (kGemmThreads / 32) / IPC;  // items per CTA at a time, warps per work item
+  const int slots = gridDim.x * ipc;
   const int n_grouped = n_items / slots * slots;
-  const int grp = warp / kWarpsPerItem, wi = warp % kWarpsPerItem;
-  for (int item = blockIdx.x * kItemsPerCta + grp; item < n_grouped; item += slots)
-    run_item<NT, XS, PUSH>(c, push, item, kWarpsPerItem, wi, grp + 1, red + size_t(grp) * kWarpsPerItem * RT * 32);
+  const int grp = warp / wpi, wi = warp % wpi;
+  for (int item = blockIdx.x * ipc + grp; item < n_grouped; item += slots)
+    run_item<NT, XS, PUSH>(c, push, item, wpi, wi, grp + 1, red + size_t(grp) * wpi * RT * 32);
   __syncthreads();
   for (int item = n_grouped + blockIdx.x; item < n_items; item += gridDim.x)
     run_item<NT, XS, PUSH>(c, push, item, kGemmThreads / 32, warp, 0, red);
@@ -425,24 +426,42 @@ __global__ void reduce_b16_kernel(const float* x, const float* scale, uint16_t* 
   y[i] = f32_to_bf16(scale ? s * scale[i % width] : s);
 }
 
+// Items a CTA works on at a time: a full round of ipc items per CTA costs about ipc units (32 warps on ipc items at
+// once), what is left after the full rounds runs one item per CTA (1 unit per round); ties go to the larger ipc
+// (longer runs of blocks per warp).
+static int gemm_items_per_cta(int n_items, int sms) {
+  int best = kMaxItemsPerCta;
+  long best_cost = 0;
+  for (int ipc = kMaxItemsPerCta; ipc >= 1; ipc >>= 1) {
+    const long ctas = min(long(sms), (long(n_items) + ipc - 1) / ipc);
+    const long full = n_items / (ctas * ipc), rest = n_items - full * ctas * ipc;  // the rest runs one item per CTA
+    const long cost = full * ipc + (rest + ctas - 1) / ctas;
+    if (ipc == kMaxItemsPerCta || cost < best_cost) best = ipc, best_cost = cost;
+  }
+  return best;
+}
+
 constexpr size_t kMaxSmem = 227 * 1024;
 static size_t gemm_smem(int nt, bool xs, int n_in) {
   return kLutBytes + size_t(32) * (xs ? 1 : nt * 8) * 32 * 4 + (xs ? size_t(n_in) * 2 : 0);
 }
-int decode_device_setup(DeviceInfo*) {
-  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               int(kMaxSmem)));
-  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               int(gemm_smem(1, false, 0))));
-  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<2, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               int(gemm_smem(2, false, 0))));
-  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               int(kMaxSmem)));
-  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               int(gemm_smem(1, false, 0))));
-  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               int(gemm_smem(2, false, 0))));
+template <int NT, bool XS, bool PUSH, int IPC>
+static int gemm_attr(size_t bytes) {
+  QB_CUDA(cudaFuncSetAttribute(trellis_gemm_kernel<NT, XS, PUSH, IPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
   return QTIP_OK;
+}
+template <bool PUSH>
+static int gemm_attrs() {
+  int rc;
+  if ((rc = gemm_attr<1, true, PUSH, 4>(kMaxSmem)) || (rc = gemm_attr<1, true, PUSH, 2>(kMaxSmem)) ||
+      (rc = gemm_attr<1, true, PUSH, 1>(kMaxSmem)))
+    return rc;
+  if ((rc = gemm_attr<1, false, PUSH, 4>(gemm_smem(1, false, 0)))) return rc;
+  return gemm_attr<2, false, PUSH, 4>(gemm_smem(2, false, 0));
+}
+int decode_device_setup(DeviceInfo*) {
+  int rc = gemm_attrs<false>();
+  return rc ? rc : gemm_attrs<true>();
 }
 
 // need_codes: the multiply and decode entry points read the trellis and the LUT; the two transforms only need the
@@ -460,21 +479,23 @@ static int multiply_impl(qtip_matrix w, const uint16_t* x, float* z, int stride,
   const DeviceInfo* info = device_info();
   if (!info) return QTIP_E_DEVICE;
   const int n_items = (w.out / 32) * splits;
-  const int ctas = min(info->sm_count, (n_items + kItemsPerCta - 1) / kItemsPerCta);
   // Up to 16 tokens per launch (two MMA column blocks in registers); larger batches walk the token axis.
   const int per = tokens <= 8 ? 8 : 16;
+  const bool one = tokens == 1 && gemm_smem(1, true, w.in) <= kMaxSmem;
+  const int ipc = one ? gemm_items_per_cta(n_items, info->sm_count) : kMaxItemsPerCta;
+  const int ctas = min(info->sm_count, (n_items + ipc - 1) / ipc);
   for (int t0 = 0; t0 < tokens; t0 += per) {
     const int nt = min(per, tokens - t0);
     push.signal = t0 + per >= tokens;  // the flags go up after the last launch of the token walk
-    if (tokens == 1 && gemm_smem(1, true, w.in) <= kMaxSmem)
-      trellis_gemm_kernel<1, true, PUSH><<<ctas, kGemmThreads, gemm_smem(1, true, w.in), s>>>(w, x, z, stride, splits,
-                                                                                            tokens, t0, nt, push);
-    else if (per == 8)
-      trellis_gemm_kernel<1, false, PUSH><<<ctas, kGemmThreads, gemm_smem(1, false, 0), s>>>(w, x, z, stride, splits,
-                                                                                            tokens, t0, nt, push);
-    else
-      trellis_gemm_kernel<2, false, PUSH><<<ctas, kGemmThreads, gemm_smem(2, false, 0), s>>>(w, x, z, stride, splits,
-                                                                                            tokens, t0, nt, push);
+#define QB_GEMM_LAUNCH(NT_, XS_, IPC_, BYTES_)                                                                      \
+  trellis_gemm_kernel<NT_, XS_, PUSH, IPC_><<<ctas, kGemmThreads, BYTES_, s>>>(w, x, z, stride, splits, tokens, t0, nt, \
+                                                                                push)
+    if (one && ipc == 4) QB_GEMM_LAUNCH(1, true, 4, gemm_smem(1, true, w.in));
+    else if (one && ipc == 2) QB_GEMM_LAUNCH(1, true, 2, gemm_smem(1, true, w.in));
+    else if (one) QB_GEMM_LAUNCH(1, true, 1, gemm_smem(1, true, w.in));
+    else if (per == 8) QB_GEMM_LAUNCH(1, false, 4, gemm_smem(1, false, 0));
+    else QB_GEMM_LAUNCH(2, false, 4, gemm_smem(2, false, 0));
+#undef QB_GEMM_LAUNCH
     QB_LAUNCHED();
   }
   return QTIP_OK;

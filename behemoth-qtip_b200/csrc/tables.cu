@@ -145,6 +145,8 @@ extern "C" int qtip_init(void) {
   if (rc) return rc;
   rc = trellis_tc_device_setup();
   if (rc) return rc;
+  rc = block_ldl_device_setup();
+  if (rc) return rc;
   info.ready = true;
   g_dev[dev] = info;
   g_dev_ready[dev].store(true, std::memory_order_release);

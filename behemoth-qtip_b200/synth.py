@@ -58,3 +58,21 @@ def spd_hessian(n, seed, rank=64):
     H = X.T @ X / N
     H += 1e-2 * np.mean(np.diag(H)) * np.eye(n)
     return H
+
+
+def reference_signs(seed, count):
+    """+-1 signs of the reference's deterministic generator (`Rng::sign`, src/common.hpp:91-107: splitmix64 seeded with
+    seed * 0x9E3779B97F4A7C15 + 0x1234567, sign = top bit of each output), so that SU / SV made here equal the
+    reference quantizer's for the same seed (SU: seed; SV of linear i: seed * 1000003 + i + 1,
+    src/quantizer.cpp:128-130,208-212)."""
+    M = (1 << 64) - 1
+    s = (seed * 0x9E3779B97F4A7C15 + 0x1234567) & M
+    out = np.empty(count, np.float32)
+    for i in range(count):
+        s = (s + 0x9E3779B97F4A7C15) & M
+        z = s
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M
+        z ^= z >> 31
+        out[i] = -1.0 if (z >> 63) else 1.0
+    return out

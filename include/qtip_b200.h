@@ -25,6 +25,7 @@ extern "C" {
 #define QTIP_E_WORKSPACE (-3) /* workspace too small */
 #define QTIP_E_DEVICE (-4)    /* device is not sm_100 or cannot run the cluster kernel */
 #define QTIP_E_KERNEL (-5)    /* a kernel reported a bounded wait that ran out (status word set) */
+#define QTIP_E_NUMERIC (-6)   /* a factorisation met a matrix that is not positive definite, or produced non-finite values */
 
 const char* qtip_last_error(void);
 /* Version of this ABI (bumped on any signature change). */
@@ -153,12 +154,49 @@ int qtip_quantize_linear(float* W_d, const float* L_d, long m, long n, const flo
                          uint16_t* Q_d, uint16_t* trellis_d, float* wscale_out, void* workspace_d, size_t workspace_bytes,
                          void* stream);
 
+/* A whole Hessian group as one call: quantize_group(s, gemm, lins, hp, opt, ...) of src/quantizer.cpp:166-346 on device
+ * buffers. The `count` linears share the rotated, damped Hessian HR_d [n][n] (qtip_rotate_hessian), its block LDL factor
+ * L_d [n][n] (qtip_block_ldl), the sign vector su_d [n] and creg; each brings its weight W_d [m][n] f32 (overwritten) and
+ * its sign vector sv_d [m]. All are rotated into WT_d [n][mt] (mt = sum of the m), quantised by ONE LDLQ + Viterbi run
+ * (hatWT_d [n][mt]; states Q_d [(mt/16)(n/16)][128], linear i's tiles starting at tile row (rows before it) / 16), and
+ * every linear gets back its Wscale, its trellis words in kernel layout, proxy_rot_reg = tr(D HR D^T) / tr(W HR W^T)
+ * and the unregularised proxy (LinearOut, src/quantizer.hpp:34-46). The traces use bf16 hi/lo splits with three partial
+ * products on the tensor cores, as the reference does with its library GEMM. Needs n % 128 == 0, every m % 32 == 0.
+ * Synchronises the stream several times (rms and traces are read back, as in the reference). Checkpoint tensors per
+ * linear: trellis_d, SU as bf16, SV * wscale (src/pipeline.cpp:329-340). */
+typedef struct qtip_group_linear {
+  float* W_d;           /* in: [m][n] f32, overwritten */
+  long m;               /* in: rows */
+  const float* sv_d;    /* in: [m] +-1 */
+  uint16_t* trellis_d;  /* out: [(m/16)(n/16)][32] u16, kernel layout */
+  float wscale;         /* out */
+  double proxy;         /* out: unregularised Hessian */
+  double proxy_rot_reg; /* out: rotated, regularised Hessian */
+} qtip_group_linear;
+size_t qtip_quantize_group_workspace_bytes(long n, long mt, long m_max);
+int qtip_quantize_group(qtip_group_linear* lins, int count, long n, const float* HR_d, const float* L_d, const float* su_d,
+                        double creg, const uint32_t* lut_h2_d, double lut_rms, double scale_override, float* WT_d,
+                        float* hatWT_d, uint16_t* Q_d, void* workspace_d, size_t workspace_bytes, void* stream);
+
 /* Hessian side of a group as one call (src/quantizer.cpp:124-152): H_d [n][n] f32 is damped in place by
  * creg = sigma_reg * mean(diag(H)) (returned through creg_out, host) and rotated, HR_d = T_n^T diag(SU) (H + creg I)
  * diag(SU) T_n. scratch_d: one double on the device. Synchronises the stream once (the trace is read back). The block LDL
  * of HR_d is the caller's (the reference computes it on the CPU in fp64, src/qtip_core.cpp:444-487). */
 int qtip_rotate_hessian(float* H_d, long n, const float* su_d, double sigma_reg, float* HR_d, double* creg_out,
                         double* scratch_d, void* stream);
+
+/* Block LDL of the rotated, damped Hessian on the GPU in fp64 (the reference does this step on the host:
+ * block_ldl_to_L / cholesky_inplace, src/qtip_core.cpp:321-487, called from ldl_hessian, src/quantizer.cpp:154-165).
+ * HR_d [n][n] f32 (the output of qtip_rotate_hessian) is symmetrised in fp64, A = (HR + HR^T) / 2, factored A = C C^T by a
+ * blocked right-looking Cholesky (128-column panels), and L_d [n][n] f32 receives the strictly block-lower factor with
+ * 16 x 16 blocks: L[:, block b] = C[:, block b] inv(C[b, b]) below the diagonal block, zero on and above it -- the L
+ * argument of qtip_ldlq. L64_d (may be NULL): the same values before the rounding to fp32. n % 16 == 0.
+ * Asynchronous on `stream`; qtip_block_ldl_status then synchronises and returns QTIP_E_NUMERIC if a pivot was not
+ * positive or the factor is not finite (the reference's `false`). */
+size_t qtip_block_ldl_workspace_bytes(long n);
+int qtip_block_ldl(const float* HR_d, long n, float* L_d, double* L64_d, void* workspace_d, size_t workspace_bytes,
+                   void* stream);
+int qtip_block_ldl_status(const void* workspace_d, void* stream);
 
 /* X_d[(tr * (n/16) + tc)][p] = W_d[16 tr + r][16 tc + c], 16 r + c = perm(p): the sequences of every 16x16 tile of a
  * row-major m x n matrix (row stride ld), i.e. what k_ldlq_prep produces block by block when the Hessian is the
@@ -181,6 +219,25 @@ int qtip_pack_trellis(const uint16_t* states_d, long B, uint16_t* packed_d, void
 int qtip_unpack_trellis(const uint16_t* packed_d, long B, uint16_t* states_d, void* stream);
 int qtip_swizzle_for_kernel(const uint16_t* packed_d, int m, int n, uint16_t* out_d, void* stream);
 int qtip_unswizzle_for_kernel(const uint16_t* in_d, int m, int n, uint16_t* packed_d, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Layer files of a QTIP checkpoint (safetensors container), host side. Writer: the tensors the quantizer emits per linear
+ * (write_layer_file, src/pipeline.cpp:314-352, container src/safetensors.cpp:93-136): `model.layers.<layer>.<name>.`
+ * trellis I16 [(m/16)(n/16), 32] (kernel layout), SU BF16 [n], SV F32 [m] (sign * Wscale), tlut F16 [512, 2], rcp I64 = 0,
+ * tp_rank I64 = 8; written to <path>.tmp and renamed. Reader: one linear with the loader's checks (load_linear,
+ * runtime/src/qtip.cpp:231-289): dtypes, shapes for the expected m x n, finite SU / SV / tlut, rcp == 0; SU comes back
+ * as fp32. All pointers are HOST pointers. */
+typedef struct qtip_checkpoint_linear {
+  const char* name;          /* e.g. "self_attn.q_proj" */
+  int m, n;                  /* out features, in features */
+  const uint16_t* trellis_h; /* (m/16)(n/16)*32 words */
+  const uint16_t* su_bf16_h; /* [n] bf16 bits */
+  const float* sv_h;         /* [m] */
+  const uint16_t* tlut_h;    /* [512][2] fp16 bits */
+} qtip_checkpoint_linear;
+int qtip_write_layer_file(const char* path, int layer, const qtip_checkpoint_linear* lins, int count);
+int qtip_read_layer_linear(const char* path, int layer, const char* name, int m, int n, uint16_t* trellis_h, float* su_h,
+                           float* sv_h, uint16_t* tlut_h);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Decode side: the runtime's QTIP linear operator. runtime/cuda/kernels.hpp:5-24, batch_kernels.hpp:5-8,22-23.

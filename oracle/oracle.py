@@ -41,7 +41,8 @@ def build(ref=False):
     if ref and root and os.path.isdir(os.path.join(root, "src")):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "REF=" + root], stderr=subprocess.DEVNULL)
         if os.path.exists(os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")):
-            subprocess.check_call(["make", "-s", "-C", _HERE, "refgpu", "REF=" + root], stderr=subprocess.DEVNULL)
+            subprocess.check_call(["make", "-s", "-C", _HERE, "refgpu", "refquant", "REF=" + root],
+                                  stderr=subprocess.DEVNULL)
 
 
 def _load(path):
@@ -396,6 +397,42 @@ class Reference:
         return y
 
 
+    # ---- layer files (safetensors): the quantizer's container writer and the runtime's loader
+    def write_layer_file(self, path, layer, linears, tlut_h):
+        """SafeTensorsWriter of the reference with write_layer_file's tensor set. linears: {name: (m, n, trellis u16, su
+        bf16 bits u16, sv f32)}."""
+        count = len(linears)
+        names = (C.c_char_p * count)(*[k.encode() for k in linears])
+        vals = list(linears.values())
+        m = (C.c_int * count)(*[v[0] for v in vals])
+        n = (C.c_int * count)(*[v[1] for v in vals])
+        keep = [[np.ascontiguousarray(v[2], np.uint16), np.ascontiguousarray(v[3], np.uint16),
+                 np.ascontiguousarray(v[4], np.float32)] for v in vals]
+        tr = (C.c_void_p * count)(*[k[0].ctypes.data for k in keep])
+        su = (C.c_void_p * count)(*[k[1].ctypes.data for k in keep])
+        sv = (C.c_void_p * count)(*[k[2].ctypes.data for k in keep])
+        tl = np.ascontiguousarray(tlut_h, np.uint16).reshape(-1)
+        self.enc.ref_write_layer_file.restype = None
+        self.enc.ref_write_layer_file.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        self.enc.ref_write_layer_file(str(path).encode(), layer, count, names, m, n, tr, su, sv, tl.ctypes.data)
+
+    def load_linear(self, path, layer, name, hidden, intermediate, kv_heads, dim, m, n):
+        """load_linear of the reference runtime on a layer file; raises ValueError with its message on a failed check."""
+        tr = np.empty(((m // 16) * (n // 16), 32), np.uint16)
+        su, sv, tl = np.empty(n, np.float32), np.empty(m, np.float32), np.empty((512, 2), np.uint16)
+        i_in, i_out = C.c_int(0), C.c_int(0)
+        f = self.dec.rref_load_linear
+        f.argtypes = [C.c_char_p, C.c_int, C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int),
+                      C.POINTER(C.c_int), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        if f(str(path).encode(), layer, name.encode(), hidden, intermediate, kv_heads, dim, C.byref(i_in), C.byref(i_out),
+             tr.ctypes.data, su.ctypes.data, sv.ctypes.data, tl.ctypes.data):
+            self.dec.rref_last_error.restype = C.c_char_p
+            raise ValueError(self.dec.rref_last_error().decode())
+        assert (i_in.value, i_out.value) == (n, m)
+        return {"trellis": tr, "SU": su, "SV": sv, "tlut": tl}
+
+
 class ReferenceGpu:
     """The reference's own CUDA kernels for this path, compiled in place for sm_100a (Makefile target `refgpu`).
 
@@ -475,3 +512,53 @@ class ReferenceGpu:
 
     def fp8_forward(self, wq, scale, x, y, n_in, n_out, stream=0):
         self._rt(self.dec.refgpu_fp8_forward(wq, scale, x, y, n_in, n_out, stream))
+
+
+class ReferenceQuant:
+    """The reference's own GPU quantizer (src/quantizer.cpp: ldlq_gpu and quantize_group, with its kernels and its
+    library-GEMM wrapper), compiled in place for sm_100a (Makefile target `refquant`). Its codebook is the one compiled
+    into the reference. `available` is False when the prebuilt file is absent."""
+
+    def __init__(self):
+        self.lib = _load(os.path.join(_HERE, "_ref", "libqtip_ref_gpu_quant.so"))
+        self.available = self.lib is not None
+        if self.lib is None:
+            return
+        P, I, L, D = C.c_void_p, C.c_int, C.c_long, C.c_double
+        self.lib.refq_ldlq_gpu.argtypes = [P, P, L, L, P, P, I, C.POINTER(D), P]
+        self.lib.refq_ldlq_gpu.restype = None
+        self.lib.refq_quantize_group.argtypes = [I, P, P, I, P, C.c_uint64, D, D, I, P, P, P, P, P, P, P, P]
+        self.lib.refq_quantize_group.restype = None
+
+    def ldlq_gpu(self, WT, L, n, m, hatWT, Q, vit_batch=1024, stream=0):
+        """Device addresses (ints). Returns the seconds the reference spent in its Viterbi kernels (it synchronises
+        around them to measure)."""
+        vit = C.c_double(0.0)
+        self.lib.refq_ldlq_gpu(WT, L, n, m, hatWT, Q, vit_batch, C.byref(vit), stream)
+        return vit.value
+
+    def quantize_group(self, weights, H, seed, sigma_reg=1e-2, scale_override=0.9, ldl_threads=8, stream=0):
+        """weights: list of [m_i, n] fp32 host arrays sharing the Hessian H [n, n] (fp32 host). Returns one dict per
+        linear (trellis, su_bf16, sv, wscale, proxy, proxy_rot_reg) and the GroupTiming fields."""
+        n = H.shape[0]
+        count = len(weights)
+        W = [np.ascontiguousarray(w, np.float32) for w in weights]
+        H = np.ascontiguousarray(H, np.float32)
+        m = (C.c_int * count)(*[w.shape[0] for w in W])
+        wp = (C.c_void_p * count)(*[w.ctypes.data for w in W])
+        tr = [np.empty((w.shape[0] // 16) * (n // 16) * 32, np.uint16) for w in W]
+        su = [np.empty(n, np.uint16) for _ in W]
+        sv = [np.empty(w.shape[0], np.float32) for w in W]
+        trp = (C.c_void_p * count)(*[a.ctypes.data for a in tr])
+        sup = (C.c_void_p * count)(*[a.ctypes.data for a in su])
+        svp = (C.c_void_p * count)(*[a.ctypes.data for a in sv])
+        wscale = np.empty(count, np.float32)
+        proxy, proxy_rr = np.empty(count, np.float64), np.empty(count, np.float64)
+        timing = np.zeros(8, np.float64)
+        self.lib.refq_quantize_group(count, m, wp, n, H.ctypes.data, seed, sigma_reg, scale_override, ldl_threads, trp, sup,
+                                     svp, wscale.ctypes.data, proxy.ctypes.data, proxy_rr.ctypes.data,
+                                     timing.ctypes.data, stream)
+        names = ("load", "rht", "ldl_cpu", "ldlq", "viterbi", "proxy", "pack", "total")
+        outs = [{"trellis": tr[i], "su_bf16": su[i], "sv": sv[i], "wscale": float(wscale[i]), "proxy": float(proxy[i]),
+                 "proxy_rot_reg": float(proxy_rr[i])} for i in range(count)]
+        return outs, dict(zip(names, timing.tolist()))

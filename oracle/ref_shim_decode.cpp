@@ -2,9 +2,12 @@
 // (runtime/src/qtip.cpp), compiled from the reference tree where it lies (see Makefile target `ref`).
 #include <cstdint>
 #include <cstring>
+#include <filesystem>
 #include <span>
+#include <string>
 #include <vector>
 
+#include "behemoth/checkpoint.hpp"
 #include "behemoth/qtip.hpp"
 
 using namespace behemoth::qtip;
@@ -58,5 +61,28 @@ int rref_forward(const uint16_t* trellis, const float* su, const float* sv, cons
     std::memcpy(y, r.data(), r.size() * 4);
     return 0;
   } catch (...) { return -1; }
+}
+// load_linear(SafeTensorFile, layer, name, config), runtime/src/qtip.cpp:231-289: the runtime's loader with its checks,
+// on a layer file at `path`; geometry from a configuration with the given hidden / intermediate / kv_heads / dim.
+// Returns 0 and fills the caller's arrays (sized from the geometry), or -1 with the message in rref_last_error().
+static thread_local std::string g_load_error;
+const char* rref_last_error() { return g_load_error.c_str(); }
+int rref_load_linear(const char* path, int layer, const char* name, int hidden, int intermediate, int kv_heads, int dim,
+                     int* in, int* out, uint16_t* trellis, float* su, float* sv, uint16_t* tlut) {
+  try {
+    behemoth::SafeTensorFile file{std::filesystem::path(path)};
+    behemoth::ModelConfig cfg;
+    cfg.hidden = hidden, cfg.intermediate = intermediate, cfg.kv_heads = kv_heads, cfg.dim = dim;
+    HostLinear l = load_linear(file, layer, name, &cfg);
+    *in = l.in, *out = l.out;
+    std::memcpy(trellis, l.trellis.data(), l.trellis.size() * 2);
+    std::memcpy(su, l.su.data(), l.su.size() * 4);
+    std::memcpy(sv, l.sv.data(), l.sv.size() * 4);
+    std::memcpy(tlut, l.tlut.data(), l.tlut.size() * 2);
+    return 0;
+  } catch (const std::exception& e) {
+    g_load_error = e.what();
+    return -1;
+  }
 }
 }

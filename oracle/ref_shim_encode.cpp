@@ -3,9 +3,11 @@
 // and as the CPU baseline; never part of the product library.
 #include <cstdint>
 #include <cstring>
+#include <string>
 #include <vector>
 
 #include "qtip_core.hpp"
+#include "safetensors.hpp"
 
 extern "C" {
 // codebook(): the reference's committed HYB table. src/qtip_core.cpp:18-50.
@@ -43,4 +45,23 @@ void ref_unpack_trellis(const uint16_t* packed, long B, uint16_t* states) { qtip
 void ref_swizzle(const uint16_t* packed, int m, int n, uint16_t* out) { qtip::swizzle_for_kernel(packed, m, n, out); }
 void ref_unswizzle(const uint16_t* in, int m, int n, uint16_t* packed) { qtip::unswizzle_for_kernel(in, m, n, packed); }
 int ref_block_ldl(double* A, int n, float* L, int threads) { return qtip::block_ldl_to_L(A, n, L, threads) ? 0 : -1; }
+// One linear's checkpoint tensors through the reference's own container writer (SafeTensorsWriter, src/safetensors.cpp:93-136),
+// with the tensor names, dtypes and shapes of write_layer_file (src/pipeline.cpp:329-340). `sv` already holds sign * Wscale.
+void ref_write_layer_file(const char* path, int layer, int count, const char* const* names, const int* m, const int* n,
+                          const uint16_t* const* trellis, const uint16_t* const* su_bf16, const float* const* sv,
+                          const uint16_t* tlut) {
+  qtip::SafeTensorsWriter w;
+  const int64_t zero = 0, eight = 8;
+  for (int i = 0; i < count; ++i) {
+    const std::string b = "model.layers." + std::to_string(layer) + "." + names[i] + ".";
+    const long tiles = long(m[i] / 16) * (n[i] / 16);
+    w.add(b + "trellis", "I16", {tiles, 32}, trellis[i], size_t(tiles) * 64);
+    w.add(b + "SU", "BF16", {n[i]}, su_bf16[i], size_t(n[i]) * 2);
+    w.add(b + "SV", "F32", {m[i]}, sv[i], size_t(m[i]) * 4);
+    w.add(b + "tlut", "F16", {512, 2}, tlut, 2048);
+    w.add(b + "rcp", "I64", {}, &zero, 8);
+    w.add(b + "tp_rank", "I64", {}, &eight, 8);
+  }
+  w.write(path);
+}
 }

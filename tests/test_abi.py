@@ -2,6 +2,8 @@
 import os
 import re
 
+import pytest
+
 from conftest import ROOT
 
 
@@ -62,3 +64,23 @@ def test_size_queries_and_host_heuristics(pkg):
     bad = pkg.QtipTpExchange()
     bad.ranks, bad.rank, bad.bytes = 9, 0, 4096
     assert lib.cdll.qtip_gathered_products(C.byref(bad), 0, C.byref(C.c_void_p())) == -1
+
+
+@pytest.mark.parametrize("unit,defines,includes", [
+    ("shim_signatures_quantizer.cpp", ["-DQTIP_CUDA"], ["src", "third_party"]),
+    ("shim_signatures_runtime.cpp", ["-DGLM53_CUDA=1"], ["runtime/cuda", "runtime/include", "glm53/include", "third_party"]),
+])
+def test_reference_side_shims_match_the_reference_headers(unit, defines, includes):
+    """The binding headers a maintainer of the reference would add (include/shims/) are compiled against the
+    reference's own headers; static_asserts compare every forwarding function's type with the declaration it replaces."""
+    import shutil
+    import subprocess
+    from conftest import REFERENCE_ROOT, ROOT
+    if not os.path.isdir(os.path.join(REFERENCE_ROOT, "src")):
+        pytest.skip("reference tree not present")
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else shutil.which("g++")
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc"))), "include")
+    cmd = [cxx, "-std=c++20", "-fsyntax-only", *defines, "-I" + os.path.join(ROOT, "include"), "-I" + cuda_inc,
+           *["-I" + os.path.join(REFERENCE_ROOT, d) for d in includes], os.path.join(ROOT, "tests", unit)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
