@@ -91,6 +91,10 @@ SIGNATURES = {
     "qtip_finish_b16": [QtipMatrix, _P, _P, _P, _I, _P, _I],
     "qtip_forward": [QtipMatrix, _P, _P, _P, _P, _P, _I, _P, _I],
     "qtip_multiply_batch": [QtipMatrix, _P, _P, _I, _I, _I, _P, _I],
+    "qtip_input_transform": [_P, _L, _P, _F, _P, _I, _I, _P, _L, _P, _P],
+    "qtip_output_residual": [_P, _I, _I, _I, _P, _I, _P, _P],
+    "qtip_output_gateup": [_P, _I, _I, _P, _P, _I, _P, _P],
+    "qtip_output_residual_input": [_P, _I, _I, _I, _P, _I, _P, _P, _F, _P, _P, _L, _P, _P],
     "qtip_decode_matrix": [QtipMatrix, _P, _P],
     "qtip_prefill_gemm": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     "qtip_prefill_gemm_splitk": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],

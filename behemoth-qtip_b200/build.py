@@ -4,7 +4,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["tables.cu", "viterbi.cu", "ldlq.cu", "hadamard.cu", "elementwise.cu", "decode.cu", "fp8.cu", "gemm_tc.cu",
+SOURCES = ["tables.cu", "viterbi.cu", "ldlq.cu", "hadamard.cu", "epilogue_residual.cu", "epilogue_gateup.cu", "elementwise.cu", "decode.cu", "fp8.cu", "gemm_tc.cu",
            "trellis_tc.cu", "block_ldl.cu", "group.cu", "checkpoint.cpp"]
 LIB = os.path.join(HERE, "libqtip_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

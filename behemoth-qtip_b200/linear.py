@@ -74,6 +74,37 @@ def qtip_forward(w, x, y, scratch, rotated, z, round_z, splits=1):
                _p(rotated, torch.bfloat16), _p(z, torch.float32), int(bool(round_z)), _stream(), splits)
 
 
+def input_transform(x, norm, epsilon, su, n, rows, u, xn=None, ldx=None, ldu=None):
+    """u = bf16(hadUt(SU (.) x')), x' = RMSNorm(x) with the runtime's rounding when `norm` (bf16 [n]) is given; xn
+    (optional) receives x'. input_transform of the reference's ROCm operator (runtime/src/qtip.hip:713-786)."""
+    init()
+    lib().call("qtip_input_transform", _p(x, torch.bfloat16), n if ldx is None else ldx, _p(norm, torch.bfloat16),
+               float(epsilon), _p(su, torch.float32), n, rows, _p(u, torch.bfloat16), n if ldu is None else ldu,
+               _p(xn, torch.bfloat16), _stream())
+
+
+def output_residual(z, splits, rows, sv, n, state, rank_major=0):
+    """state = bf16(state + bf16(SV (.) hadU(sum of the K-split partials z))): output_residual of the reference."""
+    init()
+    lib().call("qtip_output_residual", _p(z, torch.float32), splits, rows, int(rank_major), _p(sv, torch.float32), n,
+               _p(state, torch.bfloat16), _stream())
+
+
+def output_gateup(z, splits, rows, sv_gate, sv_up, features, h):
+    """h = bf16(silu(g) * u) from the stacked gate | up products z [splits, rows, 2 F]: output_gateup of the reference."""
+    init()
+    lib().call("qtip_output_gateup", _p(z, torch.float32), splits, rows, _p(sv_gate, torch.float32),
+               _p(sv_up, torch.float32), features, _p(h, torch.bfloat16), _stream())
+
+
+def output_residual_input(z, splits, rows, sv, n, state, norm, epsilon, su, u, xn=None, rank_major=0, ldu=None):
+    """output_residual, then input_transform of the updated state (output_residual_input of the reference)."""
+    init()
+    lib().call("qtip_output_residual_input", _p(z, torch.float32), splits, rows, int(rank_major), _p(sv, torch.float32), n,
+               _p(state, torch.bfloat16), _p(norm, torch.bfloat16), float(epsilon), _p(su, torch.float32),
+               _p(u, torch.bfloat16), n if ldu is None else ldu, _p(xn, torch.bfloat16), _stream())
+
+
 def qtip_multiply_batch(w, x, z, stride, splits, tokens, implementation=-1):
     init()
     lib().call("qtip_multiply_batch", w.pod, _p(x, torch.bfloat16), _p(z, torch.float32), stride, splits, tokens,

@@ -281,6 +281,37 @@ int qtip_reduce_products(float* x_d, size_t elements, int splits, void* stream);
 int qtip_reduce_to_b16(const float* x_d, const float* scale_d, uint16_t* y_d, size_t elements, int width, int splits,
                        void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------
+ * Fused epilogues of a decode step: the transforms either side of the products with the element-wise work of the
+ * residual stream folded in, one kernel each. They take the place of input_transform, output_residual, output_gateup
+ * and output_residual_input of the reference's ROCm operator (runtime/include/behemoth/qtip_gpu.hpp:199-285, kernels
+ * runtime/src/qtip.hip:713-1163), with the gathered products in this library's layouts ([split][row][n], or rank-major
+ * as qtip_finish). Hadamard orders 1, 12 and 28 (widths such as 1024, 8192, 12288, 28672). With few rows every row is
+ * spread over K CTAs (one per 1024-chunk), with many rows one CTA holds a whole row; both give the same bits.
+ *
+ * qtip_input_transform: u[r] = bf16(hadUt_n(SU (.) x'[r])), x' = bf16(x * rsqrt(mean(x^2) + epsilon) * norm) when
+ * norm_d (bf16 [n]) is given (the runtime's RMSNorm rounding), else x' = x (then it equals qtip_prepare). x_d bf16
+ * [rows][ldx], u_d bf16 [rows][ldu]; xn_d (may be NULL, needs norm_d): x' written out as bf16 [rows][n], the input of the
+ * FP8 K/V projections. */
+int qtip_input_transform(const uint16_t* x_d, long ldx, const uint16_t* norm_d, float epsilon, const float* su_d, int n,
+                         int rows, uint16_t* u_d, long ldu, uint16_t* xn_d, void* stream);
+/* qtip_output_residual: state[r] = bf16(state[r] + bf16(SV (.) hadU_n(sum over splits of z))), the o / down epilogue.
+ * z_d fp32 [splits][rows][n] (rank_major as qtip_finish), state_d bf16 [rows][n]. */
+int qtip_output_residual(const float* z_d, int splits, int rows, int rank_major, const float* sv_d, int n,
+                         uint16_t* state_d, void* stream);
+/* qtip_output_gateup: h[r] = bf16(silu(g) * u), g = bf16(SVg (.) hadU_F(bf16(zg))), u = bf16(SVu (.) hadU_F(bf16(zu))),
+ * silu(g) = g / (1 + exp(-g)). z_d fp32 [splits][rows][2 F] holds the gate products in columns [0, F) and the up
+ * products in [F, 2 F) (the stacked gate/up matrix); the sum over splits is rounded to bf16 first (the exchange
+ * rounding of these two projections). h_d bf16 [rows][F]. */
+int qtip_output_gateup(const float* z_d, int splits, int rows, const float* sv_gate_d, const float* sv_up_d, int features,
+                       uint16_t* h_d, void* stream);
+/* qtip_output_residual_input: qtip_output_residual followed by qtip_input_transform of the updated state (same width n,
+ * with the next block's norm): one kernel when the batch is large enough for whole-row CTAs, else two launches;
+ * identical results either way. */
+int qtip_output_residual_input(const float* z_d, int splits, int rows, int rank_major, const float* sv_d, int n,
+                               uint16_t* state_d, const uint16_t* norm_d, float epsilon, const float* su_d, uint16_t* u_d,
+                               long ldu, uint16_t* xn_d, void* stream);
+
 /* Prefill product on the tcgen05 tensor cores: z_d[token][row] (fp32, row stride `stride`) = sum_k w_dense_d[row][k] *
  * x_d[token][k], bf16 operands (w_dense_d is the output of qtip_decode_matrix, x_d the rotated activations). Needs
  * in % 64 == 0 and out % 128 == 0. status_d (one int, may be NULL): set to 2 if a bounded pipeline wait timed out.

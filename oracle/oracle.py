@@ -260,6 +260,40 @@ class Oracle:
             raise ValueError("unsupported Hadamard size")
         return x
 
+    # ---- fused decode-step epilogues (runtime/src/qtip.hip:713-930 of the reference), restated in numpy around the
+    # fp64 transform: where the device rounds to bf16, so does this; the transforms themselves are exact here.
+    @staticmethod
+    def _bf16(x):
+        u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+        return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
+
+    def input_transform(self, x, norm, epsilon, su):
+        """x [rows, n] (bf16 values as f32), norm [n] (bf16 values) or None -> (u, xn): input_transform_chunk."""
+        x = np.asarray(x, np.float32)
+        xn = x
+        if norm is not None:
+            factor = (1.0 / np.sqrt(np.mean(x.astype(np.float64) ** 2, axis=1) + epsilon)).astype(np.float32)
+            xn = self._bf16(x * factor[:, None] * np.asarray(norm, np.float32)[None, :])
+        u = np.stack([self.rt_hadamard(np.asarray(su, np.float64) * r, True) for r in xn.astype(np.float64)])
+        return self._bf16(u.astype(np.float32)), xn
+
+    def output_transform(self, z, sv, round_z=False):
+        """bf16(SV (.) hadU(z)) per row: the operator's output stage."""
+        z = np.asarray(z, np.float32)
+        if round_z:
+            z = self._bf16(z)
+        y = np.stack([self.rt_hadamard(r, False) for r in z.astype(np.float64)]) * np.asarray(sv, np.float64)[None, :]
+        return self._bf16(y.astype(np.float32))
+
+    def output_residual(self, z, sv, state):
+        return self._bf16(np.asarray(state, np.float32) + self.output_transform(z, sv))
+
+    def output_gateup(self, z, sv_gate, sv_up):
+        F = z.shape[1] // 2
+        g = self.output_transform(z[:, :F], sv_gate, True).astype(np.float64)
+        u = self.output_transform(z[:, F:], sv_up, True).astype(np.float64)
+        return self._bf16((g / (1.0 + np.exp(-g)) * u).astype(np.float32))
+
     def reference_forward(self, trellis, su, sv, tlut_h, n_in, n_out, x, device_rounding=False, round_z=False,
                           want_z=False):
         x = np.ascontiguousarray(x, np.float32).reshape(-1, n_in)
