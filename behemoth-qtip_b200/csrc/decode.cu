@@ -125,6 +125,31 @@ struct ItemCtx {
   int n2, in_words, stride, splits, tokens_total, t0, tokens;
 };
 
+// This warp's run of 32x32 blocks inside a work item (block-row br, K-split sp): [b_lo, b_hi).
+__device__ __forceinline__ void item_run(const ItemCtx& c, int item, int nw, int wi, int& br, int& sp, int& b_lo, int& b_hi) {
+  br = item / c.splits, sp = item - br * c.splits;
+  const int k_lo = int(long(c.n2) * sp / c.splits), k_hi = int(long(c.n2) * (sp + 1) / c.splits);
+  const int span = k_hi - k_lo;
+  b_lo = k_lo + int(long(span) * wi / nw), b_hi = k_lo + int(long(span) * (wi + 1) / nw);
+}
+// Asks the memory system to bring a warp's run of code blocks (256 bytes each, contiguous) into the L2 ahead of the loads
+// that will read it: one bulk prefetch issued by one lane, no destination, no completion to wait for. The codes are read
+// exactly once, so all the reuse there is to win is latency: the register double buffer then waits for the L2, not HBM.
+#ifndef QB_GEMV_PREFETCH
+#define QB_GEMV_PREFETCH 1
+#endif
+__device__ __forceinline__ void prefetch_run(const ItemCtx& c, int item, int n_items, int nw, int wi) {
+#if QB_GEMV_PREFETCH
+  if (item >= n_items || (threadIdx.x & 31) != 0) return;
+  int br, sp, b_lo, b_hi;
+  item_run(c, item, nw, wi, br, sp, b_lo, b_hi);
+  if (b_hi <= b_lo) return;
+  const uint2* at = c.codes + (size_t(br) * size_t(c.n2) + size_t(b_lo)) * 32u;
+  const uint32_t bytes = uint32_t(b_hi - b_lo) * 256u;
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(at), "r"(bytes) : "memory");
+#endif
+}
+
 // One work item = one 32-row block-row x one K-split, shared by `nw` warps (this is warp `wi` of them): each warp takes
 // a contiguous run of 32x32 blocks, then the partial sums are added in warp order through `red` and written to z.
 template <int NT, bool XS, bool PUSH>
@@ -133,10 +158,8 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, const TpPush& push, i
   constexpr int RT = XS ? 1 : NT * 8;  // tokens kept per warp in the reduction buffer
   const int lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
   const uint32_t lane4 = uint32_t(lane) * 4u;
-  const int br = item / c.splits, sp = item - br * c.splits;
-  const int k_lo = int(long(c.n2) * sp / c.splits), k_hi = int(long(c.n2) * (sp + 1) / c.splits);
-  const int span = k_hi - k_lo;
-  const int b_lo = k_lo + int(long(span) * wi / nw), b_hi = k_lo + int(long(span) * (wi + 1) / nw);
+  int br, sp, b_lo, b_hi;
+  item_run(c, item, nw, wi, br, sp, b_lo, b_hi);
   float acc[NT][2][4];
 #pragma unroll
   for (int t = 0; t < NT; ++t)
@@ -335,8 +358,12 @@ __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matr
   const int slots = gridDim.x * ipc;
   const int n_grouped = n_items / slots * slots;
   const int grp = warp / wpi, wi = warp % wpi;
-  for (int item = blockIdx.x * ipc + grp; item < n_grouped; item += slots)
+  prefetch_run(c, blockIdx.x * ipc + grp, n_grouped, wpi, wi);  // the first item's codes
+  for (int item = blockIdx.x * ipc + grp; item < n_grouped; item += slots) {
+    prefetch_run(c, item + slots, n_grouped, wpi, wi);  // the next item's codes travel while this one is decoded
     run_item<NT, XS, PUSH>(c, push, item, wpi, wi, grp + 1, red + size_t(grp) * wpi * RT * 32);
+  }
+  prefetch_run(c, n_grouped + blockIdx.x, n_items, kGemmThreads / 32, warp);
   __syncthreads();
   for (int item = n_grouped + blockIdx.x; item < n_items; item += gridDim.x)
     run_item<NT, XS, PUSH>(c, push, item, kGemmThreads / 32, warp, 0, red);

@@ -2,7 +2,7 @@
 //
 //  * ldlq_prep_kernel: feedback inside the current buffer, fp32 FMA with k ascending exactly as the reference's
 //    ldlq_prep_kernel (src/viterbi.hip:241-267), so the sequences handed to the Viterbi are bit-identical given
-//    identical inputs. One thread per W row j; L's 16 columns of the block staged in shared memory.
+//    identical inputs. 32 rows x 16 columns per CTA, both operand panels staged in shared memory, two chains per thread.
 //  * ldlq_update_kernel: cross-buffer update prod[r][j] += sum_k L[k][r] (WT[k][j] - hatWT[k][j]) over the 128 rows k of
 //    the finished buffer, r < c0. The reference does this with a split-bf16 library GEMM (src/quantizer.cpp:64-76); here
 //    every element is one thread's fp32 FMA chain over k ascending, which is deterministic and at least as accurate.
@@ -21,31 +21,46 @@ int quantize_tiles_impl(const float* X, int B, int b0, const uint32_t* lut, uint
                         bool two_lanes);  // viterbi.cu
 
 // Rows j in [j0, j0 + mj) of W; X is indexed from the slice start: X[(j - j0) >> 4][256].
+// A CTA owns 32 rows of W and the block's 16 columns: the (up to 112) rows of L that reach into the block and the
+// matching differences WT - hatWT of its 32 rows are staged in shared memory once (coalesced along j), then thread
+// (row, column pair) runs its two fused multiply-add chains over k ascending -- the order the reference fixes
+// (src/viterbi.hip:241-267), so every element has the reference's bits -- with conflict-free shared reads (a warp is 32
+// consecutive rows of one column pair). m / 32 CTAs of 256 threads: 48 CTAs for the 1,536-row shard of an 8-GPU split,
+// where one thread per row would leave 142 SMs idle and run 16 chains in each thread.
+constexpr int kPrepRows = 32;
 __global__ __launch_bounds__(256) void ldlq_prep_kernel(const float* __restrict__ WT, const float* __restrict__ hatWT,
                                                         const float* __restrict__ prod, const float* __restrict__ L,
                                                         long n, long m, long j0, long mj, int col0, int bufend,
                                                         float* __restrict__ X) {
   __shared__ float Ls[112][16];
+  __shared__ float Ds[112][kPrepRows];
   const int k0 = col0 + 16, nk = bufend - k0;
+  const long jb = j0 + long(blockIdx.x) * kPrepRows;
+  const long left = j0 + mj - jb;
+  const int rows = left < kPrepRows ? int(left) : kPrepRows;
   for (int idx = threadIdx.x; idx < nk * 16; idx += blockDim.x)
     Ls[idx >> 4][idx & 15] = L[long(k0 + (idx >> 4)) * n + col0 + (idx & 15)];
-  __syncthreads();
-  const long jl = long(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (jl >= mj) return;
-  const long j = j0 + jl;
-  float acc[16];
-#pragma unroll
-  for (int c = 0; c < 16; ++c) acc[c] = __fadd_rn(WT[long(col0 + c) * m + j], prod[long(col0 + c) * m + j]);
-  for (int kk = 0; kk < nk; ++kk) {
-    const long o = long(k0 + kk) * m + j;
-    const float dk = __fsub_rn(WT[o], hatWT[o]);
-#pragma unroll
-    for (int c = 0; c < 16; ++c) acc[c] = __fmaf_rn(Ls[kk][c], dk, acc[c]);
+  for (int idx = threadIdx.x; idx < nk * kPrepRows; idx += blockDim.x) {
+    const int k = idx / kPrepRows, jj = idx % kPrepRows;
+    const long o = long(k0 + k) * m + jb + jj;
+    Ds[k][jj] = jj < rows ? __fsub_rn(WT[o], hatWT[o]) : 0.f;
   }
+  __syncthreads();
+  const int jj = threadIdx.x % kPrepRows, c = 2 * (threadIdx.x / kPrepRows);
+  if (jj >= rows) return;
+  const long j = jb + jj;
+  float a0 = __fadd_rn(WT[long(col0 + c) * m + j], prod[long(col0 + c) * m + j]);
+  float a1 = __fadd_rn(WT[long(col0 + c + 1) * m + j], prod[long(col0 + c + 1) * m + j]);
+  for (int kk = 0; kk < nk; ++kk) {
+    const float dk = Ds[kk][jj];
+    a0 = __fmaf_rn(Ls[kk][c], dk, a0);
+    a1 = __fmaf_rn(Ls[kk][c + 1], dk, a1);
+  }
+  const long jl = j - j0;
   float* xb = X + (jl >> 4) * 256;
   const int r = int(jl & 15);
-#pragma unroll
-  for (int c = 0; c < 16; ++c) xb[perm_inv(r * 16 + c)] = acc[c];
+  xb[perm_inv(r * 16 + c)] = a0;
+  xb[perm_inv(r * 16 + c + 1)] = a1;
 }
 
 constexpr int kUpTile = 128, kUpK = 128, kUpKc = 16;
@@ -117,7 +132,7 @@ extern "C" int qtip_k_ldlq_prep(const float* WT_d, const float* hatWT_d, const f
   QB_REQUIRE(WT_d && hatWT_d && prod_d && L_d && X_d && n > 0 && m > 0, QTIP_E_ARG, "qtip_k_ldlq_prep: bad argument");
   QB_REQUIRE(bufend - col0 - 16 <= 112 && bufend - col0 - 16 >= 0 && col0 >= 0 && bufend <= n, QTIP_E_GEOMETRY,
              "qtip_k_ldlq_prep: block [%d, %d) is not inside a 128-column buffer", col0, bufend);
-  ldlq_prep_kernel<<<blocks_for(m, 256), 256, 0, as_stream(stream)>>>(WT_d, hatWT_d, prod_d, L_d, n, m, 0, m, col0,
+  ldlq_prep_kernel<<<blocks_for(m, kPrepRows), 256, 0, as_stream(stream)>>>(WT_d, hatWT_d, prod_d, L_d, n, m, 0, m, col0,
                                                                       bufend, X_d);
   QB_LAUNCHED();
   return QTIP_OK;
@@ -235,7 +250,7 @@ extern "C" int qtip_ldlq(const float* WT_d, const float* L_d, long n, long m, lo
         const int col0 = c0 + 16 * i;
         for (int q = 0; q < slices; ++q) {  // the same column step of every slice, each on its own stream
           const Slice& a = sl[q];
-          ldlq_prep_kernel<<<blocks_for(a.mj, 256), 256, 0, a.st>>>(WT_d, hatWT_d, prod, L_d, n, m, a.j0, a.mj, col0,
+          ldlq_prep_kernel<<<blocks_for(a.mj, kPrepRows), 256, 0, a.st>>>(WT_d, hatWT_d, prod, L_d, n, m, a.j0, a.mj, col0,
                                                                    bufend, a.X);
           QB_LAUNCHED();
           int rc = quantize_tiles_impl(a.X, a.ntr, int(a.j0 / 16), lut_h2_d, Q_d, nblk, col0 / 16, nullptr, hatWT_d, m,
