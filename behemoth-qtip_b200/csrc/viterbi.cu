@@ -429,6 +429,64 @@ __global__ void vit_finish_w_kernel(const uint32_t* __restrict__ bp, const uint1
   }
 }
 
+// The same two backtraces for launches of few sequences, where the 63 / 127 dependent global loads of the
+// one-thread-per-sequence kernels (about 0.5 us each) are the whole duration and sit on the critical path of an LDLQ
+// column step. One CTA per sequence: the 4,096 words of an 8-step block (16 KB) are staged in shared memory through a
+// ring of cp.async copies, thread 0 walks the 8 steps there, and the next blocks are in flight meanwhile; the states are
+// then emitted by 128 threads at once. Reads 128 / 256 KB per sequence instead of 63 / 127 words, which is why the
+// one-thread kernels stay for large batches. Same integer arithmetic, same outputs.
+constexpr int kBtStages = 4;
+constexpr int kBtThreads = 256;
+constexpr size_t kBtSmem = size_t(kBtStages) * 4096 * 4;
+__device__ __forceinline__ void bt_stage_block(uint32_t* dst, const uint32_t* src, int tid) {
+  const uint32_t d = smem_u32(dst) + tid * 16;
+  const char* g = reinterpret_cast<const char*>(src) + tid * 16;
+#pragma unroll
+  for (int k = 0; k < 4096 * 4 / (kBtThreads * 16); ++k)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d + k * kBtThreads * 16), "l"(g + k * kBtThreads * 16));
+}
+template <bool kFinish>
+__global__ __launch_bounds__(kBtThreads) void vit_backtrace_staged_kernel(
+    const uint32_t* __restrict__ bp, const uint16_t* __restrict__ final_state, int* __restrict__ overlap, int b0,
+    uint16_t* __restrict__ Q, int nblk, int blk, float* __restrict__ hat, float* __restrict__ hatWT, long m, int col0,
+    const uint32_t* __restrict__ lut_h2) {
+  extern __shared__ __align__(16) uint32_t bt_ring[];  // kBtStages x 4096 words
+  __shared__ uint32_t states[128];
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const uint32_t* bpb = bp + size_t(b) * 16 * 4096;
+  constexpr int kLast = kFinish ? 0 : 8;  // the overlap walk ends at step 64
+  for (int k = 0; k < kBtStages - 1; ++k) {
+    if (15 - k >= kLast) bt_stage_block(bt_ring + (k % kBtStages) * 4096, bpb + size_t(15 - k) * 4096, tid);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  uint32_t s = 0;
+  if (tid == 0) states[127] = s = final_state[b];
+  for (int q = 15; q >= kLast; --q) {
+    const int ahead = q - (kBtStages - 1);
+    if (ahead >= kLast) bt_stage_block(bt_ring + ((15 - ahead) % kBtStages) * 4096, bpb + size_t(ahead) * 4096, tid);
+    asm volatile("cp.async.commit_group;" ::: "memory");  // one group per iteration, empty at the end
+    asm volatile("cp.async.wait_group %0;" ::"n"(kBtStages - 1) : "memory");
+    __syncthreads();  // block q has landed, for every thread's copies
+    if (tid == 0) {
+      const uint32_t* w = bt_ring + ((15 - q) % kBtStages) * 4096;
+      for (int i = q == 15 ? 126 : 8 * q + 7; i >= 8 * q; --i) {
+        const uint32_t j = s >> 4;
+        s = j | (((w[j] >> (4 * (7 - (i & 7)))) & 15u) << 12);
+        states[i] = s;
+      }
+    }
+    __syncthreads();  // the buffer of block q is re-used by the copy issued in the next iteration
+  }
+  if (!kFinish) {
+    if (tid == 0) overlap[b] = int(s >> 4);
+    return;
+  }
+  if (tid < 128)
+    emit_state(tid, states[tid], Q ? Q + (size_t(b0 + b) * nblk + blk) * 128 : nullptr, hatWT, m, long(b0 + b) * 16, col0,
+               hat ? hat + size_t(b) * 256 : nullptr, lut_h2);
+}
+constexpr int kBtMaxBatch = 1024;  // launches of up to this many sequences take the staged kernels
+
 // ------------------------------------------------------------------------------------------------- host side
 
 __device__ int g_vit_status;  // time-outs of cluster launches made through the kernel-level entry point
@@ -486,6 +544,8 @@ int viterbi_device_setup(DeviceInfo* info) {
                                int(sizeof(ClusterSmem))));
   QB_CUDA(cudaFuncSetAttribute(vit_fwd_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                int(sizeof(ClusterSmem))));
+  QB_CUDA(cudaFuncSetAttribute(vit_backtrace_staged_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kBtSmem)));
+  QB_CUDA(cudaFuncSetAttribute(vit_backtrace_staged_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kBtSmem)));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(kCl * 64);
   cfg.blockDim = dim3(kClThreads);
@@ -606,12 +666,21 @@ int quantize_tiles_impl(const float* X, int B, int b0, const uint32_t* lut, uint
       uint32_t* bp = w.bp + size_t(o) * (kBpBytes / 4);
       int rc = launch_cluster_fwd(info, xc, nullptr, 1, nb, bp, 8, w.fs + o, lut, w.status, st);
       if (rc) return rc;
-      vit_overlap_w_kernel<<<blocks_for(nb, 64), 64, 0, st>>>(bp, w.fs + o, nb, w.ov + o);
+      if (nb <= kBtMaxBatch)
+        vit_backtrace_staged_kernel<false><<<nb, kBtThreads, kBtSmem, st>>>(bp, w.fs + o, w.ov + o, 0, nullptr, 0, 0, nullptr,
+                                                                           nullptr, 0, 0, nullptr);
+      else
+        vit_overlap_w_kernel<<<blocks_for(nb, 64), 64, 0, st>>>(bp, w.fs + o, nb, w.ov + o);
       QB_LAUNCHED();
       rc = launch_cluster_fwd(info, xc, w.ov + o, 0, nb, bp, 0, w.fs + o, lut, w.status, st);
       if (rc) return rc;
-      vit_finish_w_kernel<<<blocks_for(nb, 64), 64, 0, st>>>(bp, w.fs + o, nb, b0 + c0, Q, nblk, blk,
-                                                             hat ? hat + size_t(c0) * 256 : nullptr, hatWT, m, col0, lut);
+      float* hc = hat ? hat + size_t(c0) * 256 : nullptr;
+      if (nb <= kBtMaxBatch)
+        vit_backtrace_staged_kernel<true><<<nb, kBtThreads, kBtSmem, st>>>(bp, w.fs + o, nullptr, b0 + c0, Q, nblk, blk, hc,
+                                                                          hatWT, m, col0, lut);
+      else
+        vit_finish_w_kernel<<<blocks_for(nb, 64), 64, 0, st>>>(bp, w.fs + o, nb, b0 + c0, Q, nblk, blk, hc, hatWT, m, col0,
+                                                               lut);
       QB_LAUNCHED();
     }
     return QTIP_OK;

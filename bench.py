@@ -260,7 +260,7 @@ def main():
                          "with a synthetic correlated Hessian (secondary line); layer: the products of one layer; "
                          "kernel: a few launches of one kernel on a small case (for profiler captures)")
     ap.add_argument("--ldlq-shape", default="12288x28672", help="m x n of the ldlq workload")
-    ap.add_argument("--kernel", default="gemv", choices=["viterbi", "gemv", "fused", "prefill"],
+    ap.add_argument("--kernel", default="gemv", choices=["viterbi", "gemv", "fused", "prefill", "epilogue"],
                     help="--workload kernel: which kernel")
     ap.add_argument("--size", type=int, default=16384, help="--workload kernel: sequences (viterbi) or output rows")
     ap.add_argument("--tokens", type=int, default=0, help="--workload kernel: token count (fused: 64, prefill: 2048)")
@@ -813,11 +813,15 @@ def layer_section(ctx):
         check = _unsharded_reference(linear, w, xs[hidden], T, torch)
         q_err = float((ys[hidden].float() - check.float()).norm() / check.float().norm())
         del check
-        us = _graph_us(layer, 2, torch) if T <= 512 else _time_us(layer, 3, torch)
-        saved, w8_all = w8[:], w8
-        del w8[:]  # the same schedule without the FP8 K/V projections: the number the reference leg is compared with
-        lin_us = _graph_us(layer, 2, torch) if T <= 512 else _time_us(layer, 3, torch)
-        w8_all.extend(saved)
+        # Prefill-sized batches run at the power cap and the clock sags over the first seconds of load: both schedules
+        # are timed twice, alternating, and the faster pass of each is kept, so that the two numbers see the same clocks.
+        timed = (lambda: _graph_us(layer, 2, torch)) if T <= 512 else (lambda: _time_us(layer, 3, torch))
+        saved, us, lin_us = w8[:], float("inf"), float("inf")
+        for _ in range(1 if T <= 512 else 2):
+            us = min(us, timed())
+            del w8[:]  # the same schedule without the FP8 K/V projections: the number the reference leg is compared with
+            lin_us = min(lin_us, timed())
+            w8.extend(saved)
         flops = 2.0 * T * weights
         out["T%d" % T] = {"layer_us": us, "linears_us": lin_us, "code_gbs": code_bytes / us / 1e3,
                           "tflops": flops / us / 1e6,
@@ -922,6 +926,8 @@ def kernel_workload(args):
         su, sv = torch.from_numpy(synth.signs(n_in, 7)).cuda(), torch.from_numpy(synth.signs(n_out, 8)).cuda()
         return linear.Matrix(trellis, su, sv, linear.runtime_lut(synth.seeded_tlut(1)), n_in, n_out)
 
+    if args.kernel == "epilogue":
+        return print(json.dumps(epilogue_timings(torch, pkg, args.tokens or 64)))
     if args.kernel == "viterbi":
         lut_d, _ = codec.device_lut(synth.seeded_tlut(1))
         X = torch.randn(size, 256, generator=gen, device="cuda")
@@ -957,6 +963,54 @@ def kernel_workload(args):
     linear.kernel_status()
     print(json.dumps({"workload": "kernel", "kernel": args.kernel, "size": size, "tokens": args.tokens,
                       "splits": args.splits, "us_per_launch": e0.elapsed_time(e1) * 1e3 / 3}))
+
+
+def epilogue_timings(torch, pkg, rows):
+    """GPU time (CUDA-graph replay) of the fused decode-step epilogues beside the unfused stages they replace, at the
+    layer's widths (hidden 12288, intermediate 28672) for `rows` tokens."""
+    linear, synth = pkg.linear, pkg.synth
+    hidden, inter = 12288, 28672
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    bf = lambda *shape: torch.randn(*shape, generator=g, device="cuda").to(torch.bfloat16)  # noqa: E731
+    su_h, su_i = (torch.from_numpy(synth.signs(n, 7)).cuda() for n in (hidden, inter))
+    sv_h, sv_i = (torch.from_numpy(synth.signs(n, 8)).cuda() * 0.02 for n in (hidden, inter))
+    norm = (1.0 + 0.1 * bf(hidden).float()).to(torch.bfloat16)
+    x, state = bf(rows, hidden), bf(rows, hidden)
+    u, xn, y = (torch.empty(rows, hidden, dtype=torch.bfloat16, device="cuda") for _ in range(3))
+    z_h = torch.randn(1, rows, hidden, generator=g, device="cuda")
+    z_gu = torch.randn(1, rows, 2 * inter, generator=g, device="cuda")
+    z_g, z_u = z_gu[0, :, :inter].contiguous(), z_gu[0, :, inter:].contiguous()
+    h, yg, yu = (torch.empty(rows, inter, dtype=torch.bfloat16, device="cuda") for _ in range(3))
+    scratch = torch.empty(1, device="cuda")
+    w_h = linear.Matrix(None, su_h, sv_h, None, hidden, hidden)
+    w_i = linear.Matrix(None, su_i, sv_i, None, inter, inter)
+
+    def unfused_gateup():
+        linear.qtip_finish(w_i, z_g, yg, scratch, True, 1, rows)
+        linear.qtip_finish(w_i, z_u, yu, scratch, True, 1, rows)
+        gf = yg.float()
+        torch.mul(gf / (1.0 + torch.exp(-gf)), yu.float(), out=gf)
+        h.copy_(gf)
+
+    def unfused_residual_input():
+        linear.qtip_finish(w_h, z_h, y, scratch, False, 1, rows)
+        state.add_(y)
+        xf = state.float()
+        xn.copy_(xf * torch.rsqrt((xf * xf).mean(dim=1, keepdim=True) + 1e-5) * norm.float())
+        linear.qtip_prepare(w_h, xn, scratch, u, rows)
+
+    t = lambda fn: _graph_us(fn, 4, torch)  # noqa: E731
+    return {"workload": "kernel", "kernel": "epilogue", "rows": rows,
+            "input_transform_with_norm_us": t(lambda: linear.input_transform(x, norm, 1e-5, su_h, hidden, rows, u, xn)),
+            "prepare_alone_us": t(lambda: linear.qtip_prepare(w_h, x, scratch, u, rows)),
+            "output_residual_us": t(lambda: linear.output_residual(z_h, 1, rows, sv_h, hidden, state)),
+            "finish_alone_us": t(lambda: linear.qtip_finish(w_h, z_h, y, scratch, False, 1, rows)),
+            "output_residual_input_us": t(lambda: linear.output_residual_input(z_h, 1, rows, sv_h, hidden, state, norm,
+                                                                                1e-5, su_h, u, xn)),
+            "finish_add_norm_prepare_unfused_us": t(unfused_residual_input),
+            "output_gateup_us": t(lambda: linear.output_gateup(z_gu, 1, rows, sv_i, sv_i, inter, h)),
+            "two_finishes_and_silu_unfused_us": t(unfused_gateup)}
 
 
 def _time_us(fn, iters, torch):

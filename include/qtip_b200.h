@@ -181,7 +181,7 @@ int qtip_quantize_group(qtip_group_linear* lins, int count, long n, const float*
 /* Hessian side of a group as one call (src/quantizer.cpp:124-152): H_d [n][n] f32 is damped in place by
  * creg = sigma_reg * mean(diag(H)) (returned through creg_out, host) and rotated, HR_d = T_n^T diag(SU) (H + creg I)
  * diag(SU) T_n. scratch_d: one double on the device. Synchronises the stream once (the trace is read back). The block LDL
- * of HR_d is the caller's (the reference computes it on the CPU in fp64, src/qtip_core.cpp:444-487). */
+ * of HR_d is the next step: qtip_block_ldl below, or the reference's host routine (src/qtip_core.cpp:444-487). */
 int qtip_rotate_hessian(float* H_d, long n, const float* su_d, double sigma_reg, float* HR_d, double* creg_out,
                         double* scratch_d, void* stream);
 

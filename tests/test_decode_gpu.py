@@ -188,10 +188,13 @@ def test_fp8_kv_projection(gpu, oracle, tokens):
             assert rel_l2(y2.float().cpu().numpy(), ref_b[:, :128]) < 4e-3
 
 
-@pytest.mark.parametrize("n_in,n_out,tokens", [(512, 256, 300), (1024, 128, 256), (12288, 384, 17)])
+@pytest.mark.parametrize("n_in,n_out,tokens", [(512, 256, 300), (1024, 128, 256), (12288, 384, 17), (1024, 1536, 520),
+                                               (512, 4096, 2560), (1024, 4096, 2560)])
 def test_prefill_gemm_tensor_cores(gpu, n_in, n_out, tokens):
     """tcgen05 product against float64 on the same bf16 operands: fp32 accumulation, rel-L2 <= 5e-5 (K up to 12,288
-    terms per output); ragged token counts (rows past the end are not written)."""
+    terms per output); ragged token counts (rows past the end are not written). The shapes cover the tile-per-CTA launch
+    (1 and 2 tiles), the persistent launch with tiles split 8 ways (2 tiles, one of them half a tile high) and 2 ways
+    (18 tiles), with whole-tile rounds only (160 tiles, 8 K steps) and with whole-tile rounds plus 12 split tiles."""
     rng = np.random.default_rng(n_in + tokens)
     wb = gpu.synth.f32_to_bf16_bits(rng.standard_normal((n_out, n_in)).astype(np.float32))
     xb = gpu.synth.f32_to_bf16_bits(rng.standard_normal((tokens, n_in)).astype(np.float32))
@@ -203,6 +206,28 @@ def test_prefill_gemm_tensor_cores(gpu, n_in, n_out, tokens):
     ref = gpu.synth.bf16_bits_to_f32(xb).astype(np.float64) @ gpu.synth.bf16_bits_to_f32(wb).astype(np.float64).T
     assert rel_l2(z[:tokens].cpu().numpy(), ref) < 5e-5
     assert bool((z[tokens:] == 7.0).all())
+
+
+def test_prefill_gemm_split_tiles_are_reproducible(gpu):
+    """A product whose tiles are split over several CTAs and summed in the output: 40 launches give the same bits (the
+    order of the additions is fixed) and the library's ring of state blocks wraps around without being cleared."""
+    n_in, n_out, tokens = 1024, 1536, 520
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4)
+    w = torch.randn(n_out, n_in, generator=g, device="cuda").to(torch.bfloat16)
+    x = torch.randn(tokens, n_in, generator=g, device="cuda").to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    first = None
+    for _ in range(40):
+        z = torch.full((tokens, n_out), float("nan"), dtype=torch.float32, device="cuda")
+        gpu.linear.prefill_gemm(w, x, z, n_out, n_in, n_out, tokens, status)
+        if first is None:
+            first = z
+            ref = x.double() @ w.double().T
+            assert float((z.double() - ref).norm() / ref.norm()) < 5e-5
+        else:
+            assert torch.equal(z, first)
+    assert int(status) == 0
 
 
 def test_multiply_prefill_matches_batch_path(gpu, oracle):
