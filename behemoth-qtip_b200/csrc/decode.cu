@@ -75,11 +75,7 @@ __device__ __forceinline__ uint32_t lut_word(uint32_t v, uint32_t lane4) {
   const uint32_t y = v * v + v;
   const uint32_t at = (((y >> 6) & 1023u) << 7) + lane4;
 #endif
-#if defined(QB_GEMV_ABLATE) && QB_GEMV_ABLATE == 1
-  return at;
-#else
   return *reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(gemm_smem_words) + at);
-#endif
 }
 __device__ __forceinline__ void decode_pair(uint32_t o, uint32_t p, uint32_t lane4, uint32_t (&lo)[4],
                                             uint32_t (&hi)[4]) {
@@ -205,11 +201,7 @@ __device__ __forceinline__ void run_item(const ItemCtx& c, const TpPush& push, i
       for (int i1 = 0; i1 < 2; ++i1)
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-#if defined(QB_GEMV_ABLATE) && QB_GEMV_ABLATE == 2
-          acc[t][i1][0] = __uint_as_float(__float_as_uint(acc[t][i1][0]) ^ a[i1][0] ^ a[i1][1] ^ a[i1][2] ^ a[i1][3] ^ bw[t][2 * j1]);
-#else
           mma_bf16_16816(acc[t][i1], a[i1], bw[t][2 * j1], bw[t][2 * j1 + 1]);
-#endif
         }
     }
   };

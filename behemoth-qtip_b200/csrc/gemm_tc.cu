@@ -25,9 +25,6 @@
 
 namespace qb {
 
-#ifndef QB_SK_ABLATE
-#define QB_SK_ABLATE 0  // timing experiments only: 1 = no global stores in the stream-K epilogue, 2 = no TMEM reads either
-#endif
 #ifndef QB_TC_RASTER
 #define QB_TC_RASTER 1
 #endif
@@ -375,21 +372,12 @@ __global__ __launch_bounds__(kTcThreads, 1) void gemm_tc_streamk_kernel(const __
 #pragma unroll
           for (int c = 0; c < 32; ++c) sum[c] = c < live ? __ldcg(at + size_t(c) * stride) : 0.f;
         }
-#if QB_SK_ABLATE == 2
-        if (cc > 100000) {
-#endif
         tc_tmem_ld32(tmem + (uint32_t(q * 32) << 16) + uint32_t(cc), v);
 #pragma unroll
         for (int c = 0; c < 32; ++c) sum[c] = add ? sum[c] + __uint_as_float(v[c]) : __uint_as_float(v[c]);
-#if QB_SK_ABLATE == 1
-        if (sum[0] == 1.2345f)
-#endif
 #pragma unroll
         for (int c = 0; c < 32; ++c)
           if (c < live) at[size_t(c) * stride] = sum[c];
-#if QB_SK_ABLATE == 2
-        }
-#endif
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       tc_mbar_arrive(smem_u32(&sm.acc_empty));  // 128 arrivals: the accumulator may be overwritten

@@ -315,7 +315,11 @@ int qtip_output_residual_input(const float* z_d, int splits, int rows, int rank_
 /* Prefill product on the tcgen05 tensor cores: z_d[token][row] (fp32, row stride `stride`) = sum_k w_dense_d[row][k] *
  * x_d[token][k], bf16 operands (w_dense_d is the output of qtip_decode_matrix, x_d the rotated activations). Needs
  * in % 64 == 0 and out % 128 == 0. status_d (one int, may be NULL): set to 2 if a bounded pipeline wait timed out.
- * Replaces the cublasGemmEx call of the >= 128-token path (runtime/cuda/tensor_model.cpp:210-222). */
+ * Replaces the cublasGemmEx call of the >= 128-token path (runtime/cuda/tensor_model.cpp:210-222).
+ * Products of more than a few tiles run as one persistent cooperative launch (one CTA per SM) in which the tiles of the
+ * last, partial round are split by K ranges and summed in z in a fixed order, so results are reproducible run to run;
+ * the per-tile counters of that sum live in a ring of 32 state blocks inside the library, one per launch, so up to 32
+ * such products may be in flight on one GPU at a time (streams, graph branches). Capturable; no allocation. */
 int qtip_prefill_gemm(const uint16_t* w_dense_d, const uint16_t* x_d, float* z_d, int stride, int in, int out, int tokens,
                       int* status_d, void* stream);
 /* The same product with the K range split `splits` ways over the grid, for weights with few rows (the FP8 K/V

@@ -230,6 +230,33 @@ def test_prefill_gemm_split_tiles_are_reproducible(gpu):
     assert int(status) == 0
 
 
+def test_prefill_gemm_replays_from_a_cuda_graph(gpu):
+    """The persistent launch (cooperative, with its counters inside the library) captured once and replayed: every replay
+    gives the bits of the eager call (the counters are versioned by an epoch the kernel itself advances)."""
+    n_in, n_out, tokens = 1024, 1536, 520
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    w = torch.randn(n_out, n_in, generator=g, device="cuda").to(torch.bfloat16)
+    x = torch.randn(tokens, n_in, generator=g, device="cuda").to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    eager = torch.zeros((tokens, n_out), dtype=torch.float32, device="cuda")
+    gpu.linear.prefill_gemm(w, x, eager, n_out, n_in, n_out, tokens, status)
+    z = torch.zeros((tokens, n_out), dtype=torch.float32, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            gpu.linear.prefill_gemm(w, x, z, n_out, n_in, n_out, tokens, status)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        z.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(z, eager)
+    assert int(status) == 0
+
+
 def test_multiply_prefill_matches_batch_path(gpu, oracle):
     n_in, n_out, tokens = 1024, 256, 200
     w, tr, su, sv, tl = make_linear(gpu, n_in, n_out, 90)
