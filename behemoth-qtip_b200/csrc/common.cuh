@@ -76,4 +76,25 @@ __device__ __forceinline__ uint32_t lut_entry(uint32_t s) {
 
 inline unsigned blocks_for(long n, int per) { return unsigned((n + per - 1) / per); }
 
+// Programmatic dependent launch for the chains of short kernels of a decode step (input transform, product, output
+// transform, ...): a kernel launched through launch_chained() may become resident while the kernel before it in the
+// stream is still draining, runs whatever does not depend on that kernel (table set-up), and blocks in
+// chain_wait() until the earlier kernel has completed and its writes are visible. Every kernel of a chain calls
+// chain_release() first (its successor may then be scheduled as SMs free up) and chain_wait() before its first read
+// of an activation or first write of an output. Without the launch attribute both calls do nothing.
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+bool chained_launches_enabled();  // QTIP_PDL=0 turns the attribute off (plain stream order), tables.cu
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = s;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = chained_launches_enabled() ? 1 : 0;
+  cfg.attrs = &attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 }  // namespace qb

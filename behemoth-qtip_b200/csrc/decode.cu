@@ -321,6 +321,7 @@ __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matr
   float* red = reinterpret_cast<float*>(smem + kLutBytes);  // [32 warps][RT tokens][32 rows]
   uint32_t* xs = reinterpret_cast<uint32_t*>(smem + kLutBytes + 32 * RT * 32 * 4);
   const int tid = threadIdx.x, warp = tid >> 5;
+  chain_release();  // the output transform behind this launch may be scheduled as SMs free up
   {
     // 32 copies of the table: each thread reads ONE entry from global memory, a warp then spreads its 32 entries with
     // shuffles so that every store instruction writes 32 consecutive words (no bank conflicts, one load latency).
@@ -333,6 +334,7 @@ __global__ __launch_bounds__(kGemmThreads, 1) void trellis_gemm_kernel(qtip_matr
       for (int e = 0; e < 32; ++e) lut_s[(e0 + e) * 32 + lane] = __shfl_sync(0xffffffffu, mine, e);
     }
   }
+  chain_wait();  // the table above does not depend on the kernel before this one; the activations and z do
   const uint32_t* xw = reinterpret_cast<const uint32_t*>(x) + size_t(t0) * (w.in / 2);
   if constexpr (XS) {
     for (int i = tid; i < w.in / 2; i += kGemmThreads) {
@@ -510,8 +512,8 @@ static int multiply_impl(qtip_matrix w, const uint16_t* x, float* z, int stride,
     const int nt = min(per, tokens - t0);
     push.signal = t0 + per >= tokens;  // the flags go up after the last launch of the token walk
 #define QB_GEMM_LAUNCH(NT_, XS_, IPC_, BYTES_)                                                                      \
-  trellis_gemm_kernel<NT_, XS_, PUSH, IPC_><<<ctas, kGemmThreads, BYTES_, s>>>(w, x, z, stride, splits, tokens, t0, nt, \
-                                                                                push)
+  QB_CUDA(launch_chained(trellis_gemm_kernel<NT_, XS_, PUSH, IPC_>, dim3(ctas), dim3(kGemmThreads), BYTES_, s, w, x, z, \
+                         stride, splits, tokens, t0, nt, push))
     if (one && ipc == 4) QB_GEMM_LAUNCH(1, true, 4, gemm_smem(1, true, w.in));
     else if (one && ipc == 2) QB_GEMM_LAUNCH(1, true, 2, gemm_smem(1, true, w.in));
     else if (one) QB_GEMM_LAUNCH(1, true, 1, gemm_smem(1, true, w.in));

@@ -27,6 +27,8 @@ __global__ __launch_bounds__(256) void fp8_gemv_kernel(const uint8_t* __restrict
   float acc[kFp8Tokens];
 #pragma unroll
   for (int t = 0; t < kFp8Tokens; ++t) acc[t] = 0.f;
+  chain_release();
+  chain_wait();  // x may come from the kernel before this one, y may still be read by it
   if (row < out) {
     const int chunks = in / 16, c_lo = chunks * quarter / kFp8Split, c_hi = chunks * (quarter + 1) / kFp8Split;
     const uint4* wr = reinterpret_cast<const uint4*>(w + size_t(row) * in);
@@ -117,7 +119,7 @@ extern "C" int qtip_fp8_forward(const uint8_t* w_d, const float* scale_d, const 
   QB_REQUIRE(in > 0 && out > 0 && in % 16 == 0, QTIP_E_GEOMETRY, "qtip_fp8_forward: in = %d must be a multiple of 16", in);
   const dim3 grid(blocks_for(out, 2), blocks_for(tokens, kFp8Tokens));
   QB_REQUIRE(grid.y <= 65535, QTIP_E_GEOMETRY, "qtip_fp8_forward: too many tokens (%d)", tokens);
-  fp8_gemv_kernel<<<grid, 256, 0, as_stream(stream)>>>(w_d, scale_d, x_d, y_d, in, out, tokens);
+  QB_CUDA(launch_chained(fp8_gemv_kernel, grid, dim3(256), 0, as_stream(stream), w_d, scale_d, x_d, y_d, in, out, tokens));
   QB_LAUNCHED();
   return QTIP_OK;
 }

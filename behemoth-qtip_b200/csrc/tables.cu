@@ -2,6 +2,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <atomic>
 #include <mutex>
@@ -119,6 +120,16 @@ static uint16_t float_to_bf16_bits(float f) {
 }  // namespace qb
 
 using namespace qb;
+
+namespace qb {
+bool chained_launches_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("QTIP_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+}  // namespace qb
 
 extern "C" const char* qtip_last_error(void) { return g_error; }
 extern "C" int qtip_abi_version(void) { return 1; }
