@@ -957,7 +957,33 @@ def reference_layer(ctx, mats, w8, s8):
         out["T%d" % T] = {"linears_us": total, "per_linear": per}
         del xs, rot, ys, scratch, z
     out["kind"] = "the reference's CUDA kernels recompiled for sm_100a, same GPU, same codes; QTIP linears only (no FP8 K/V)"
+    try:
+        out["cpu_q_proj_16_tokens"] = cpu_q_proj(ctx, mats["q"])
+    except Exception as ex:
+        out["cpu_q_proj_16_tokens"] = {"error": repr(ex)}
     return out
+
+
+def cpu_q_proj(ctx, w, tokens=16):
+    """Reported CPU baseline of the batched products: the reference's CPU reference_forward (runtime/src/qtip.cpp:129-192,
+    compiled in place, OpenMP, double accumulation, device rounding) on the q projection at 16 tokens, beside this
+    library's operator on the same input. Test infrastructure."""
+    from oracle.oracle import Oracle, Reference
+    torch, pkg = ctx.torch, ctx.pkg
+    linear, synth = pkg.linear, pkg.synth
+    R = Reference()
+    fwd, kind = (R.reference_forward, "reference") if R.available else (Oracle().reference_forward, "port")
+    g = torch.Generator(device="cuda")
+    g.manual_seed(16)
+    x = torch.randn(tokens, w.n_in, generator=g, device="cuda").to(torch.bfloat16)
+    t0 = time.perf_counter()
+    out = fwd(w.trellis.cpu().numpy().view(np.uint16), w.su.cpu().numpy(), w.sv.cpu().numpy(),
+              synth.seeded_tlut(1).view(np.uint16), w.n_in, w.n_out, x.float().cpu().numpy(), True, False)
+    dt = time.perf_counter() - t0
+    yc = np.asarray(out[0] if isinstance(out, tuple) else out, dtype=np.float64).reshape(tokens, w.n_out)
+    ours = _unsharded_reference(linear, w, x, tokens, torch).float().cpu().numpy().astype(np.float64)
+    return {"kind": kind, "cores": len(os.sched_getaffinity(0)), "seconds": dt, "tokens": tokens,
+            "rel_l2_of_this_library": float(np.linalg.norm(ours - yc) / np.linalg.norm(yc))}
 
 
 def kernel_workload(args):
