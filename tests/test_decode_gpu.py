@@ -74,7 +74,8 @@ def test_multiply_against_decoded_weights(gpu, oracle, n_in, n_out, splits):
 @pytest.mark.parametrize("n_in,n_out", [(384, 256), (1024, 384), (12288, 1024), (3584, 12288 // 8)])
 def test_forward_against_reference_linear(gpu, oracle, n_in, n_out):
     """prepare + multiply + finish vs reference_forward(device_rounding = true). bf16 outputs against the bf16-rounded
-    reference: rel-L2 < 1e-2 (one bf16 ulp is 4e-3); the fp32 products z against the oracle's z: rel-L2 <= 1e-3."""
+    reference: rel-L2 < 4e-3 (one bf16 rounding; 1e-2 when z is rounded to bf16 first); the fp32 products z against the
+    oracle's z: rel-L2 <= 1e-3."""
     w, tr, su, sv, tl = make_linear(gpu, n_in, n_out, 50, sv_scale=0.003)
     x = (np.random.default_rng(9).standard_normal(n_in) * 0.1).astype(np.float32)
     xb = gpu.synth.f32_to_bf16_bits(x)
@@ -90,7 +91,9 @@ def test_forward_against_reference_linear(gpu, oracle, n_in, n_out):
         if not round_z:
             assert rel_l2(zz, zo[0]) < 1e-3
         yo_b = gpu.synth.bf16_bits_to_f32(gpu.synth.f32_to_bf16_bits(yo[0]))
-        assert rel_l2(y.float().cpu().numpy(), yo_b) < 1e-2
+        # one bf16 rounding of the output (2^-8); with round_z the bf16 rounding of z can also flip where the fp32 and
+        # the double sums straddle a rounding boundary
+        assert rel_l2(y.float().cpu().numpy(), yo_b) < (1e-2 if round_z else 4e-3)
         assert np.abs(y.float().cpu().numpy() - yo_b).max() < 0.03 * np.abs(yo_b).max()
 
 
