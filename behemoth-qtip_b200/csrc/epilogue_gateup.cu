@@ -41,8 +41,10 @@ int hadamard_output_gateup(const float* z, int splits, long split_stride, int ro
   QB_REQUIRE(rows <= 65535, QTIP_E_GEOMETRY, "too many rows");
   const int threads = a.P >= 1024 ? 1024 : (a.P < 64 ? 64 : a.P);
   const size_t chunk_smem = (size_t(a.P > 1024 ? a.P : 1024) + a.P) * 4, row_smem = size_t(F) * 8;
-#define QB_GATEUP(K_)                                                                                        \
-  if (chunks) had_chunk_gateup_kernel<K_><<<dim3(K_, unsigned(rows)), threads, chunk_smem, s>>>(a, sv_up); \
+  // few rows: a link of a decode step's kernel chain (programmatic dependent launch, like the other chunk kernels)
+#define QB_GATEUP(K_)                                                                                                  \
+  if (chunks)                                                                                                          \
+    QB_CUDA(launch_chained(had_chunk_gateup_kernel<K_>, dim3(K_, unsigned(rows)), dim3(threads), chunk_smem, s, a, sv_up)); \
   else had_row_gateup_kernel<K_><<<unsigned(rows), 1024, row_smem, s>>>(a, sv_up)
   switch (K) {
     case 1: had_row_gateup_kernel<1><<<unsigned(rows), 1024, row_smem, s>>>(a, sv_up); break;

@@ -461,6 +461,8 @@ __global__ __launch_bounds__(1024, 1) void had_chunk_gateup_kernel(HadArgs a, co
   const long row = blockIdx.y;
   const int work = a.P > 1024 ? a.P : 1024;
   a.aux = row_s + work, a.aux_base = r * a.P;
+  chain_release();
+  chain_wait();
 #pragma unroll 1
   for (int phase = 0; phase < 2; ++phase) {
     a.phase = phase;

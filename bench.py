@@ -893,10 +893,112 @@ def layer_section(ctx):
            "config": {"workload": "mistral_large_layer_products", "hidden": hidden, "intermediate": inter,
                       "code_bytes": code_bytes, "weights": weights, "peaks": peak_src}, "tokens": out}
     try:
+        res["decode_step_fused"] = decode_step_fused(ctx, mats, w8, s8)
+    except Exception as ex:
+        res["decode_step_fused"] = {"error": repr(ex)}
+    try:
         res["reference_gpu"] = reference_layer(ctx, mats, w8, s8)
     except Exception as ex:
         res["reference_gpu"] = {"error": repr(ex)}
     return res
+
+
+def decode_step_fused(ctx, mats, w8, s8):
+    """The same layer as a decode step with the fused epilogues, at 1 and 16 tokens: RMSNorm + input transform (the
+    normalised row also feeds the FP8 K/V projections), q; o with the residual add and the next RMSNorm + input transform
+    in its epilogue; gate and up as ONE product over the stacked 57,344-row matrix with SiLU(gate) * up in its epilogue;
+    down with the residual add. Besides the products of `layer_us` this does both norms, both residual adds and the
+    activation (the attention between q/k/v and o is outside the path: o reads a stand-in input). CUDA-graph replay."""
+    torch, pkg = ctx.torch, ctx.pkg
+    linear = pkg.linear
+    hidden, inter, kv, eps = 12288, 28672, 1024, 1e-5
+    q, o, gate, up, down = (mats[k] for k in ("q", "o", "gate", "up", "down"))
+    gu = linear.Matrix(torch.cat([gate.trellis, up.trellis]), gate.su, torch.cat([gate.sv, up.sv]), gate.lut, hidden, 2 * inter)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(21)
+    out = {}
+    for T in (1, 16):
+        bf = lambda *shape: (0.05 * torch.randn(*shape, generator=g, device="cuda")).to(torch.bfloat16)  # noqa: E731
+        state, attn = bf(T, hidden), bf(T, hidden)
+        norm1, norm2 = ((1.0 + bf(hidden).float()).to(torch.bfloat16) for _ in range(2))
+        u_h, xn, u_o, y_q = (torch.empty(T, hidden, dtype=torch.bfloat16, device="cuda") for _ in range(4))
+        h, u_d = (torch.empty(T, inter, dtype=torch.bfloat16, device="cuda") for _ in range(2))
+        y_kv = torch.empty(T, kv, dtype=torch.bfloat16, device="cuda")
+        # K-splits as in the unfused schedule: the tensor-core kernel's own choice where the batch takes it, else two for
+        # the 12,288-row products and one for the wide one
+        sp = {w: (linear.tc_splits(w.n_out) if T > 1 and linear.batch_uses_tc(w.n_in, w.n_out, T) else
+                  (2 if w.n_out == hidden else 1)) for w in (q, o, gu, down)}
+        z_h = torch.empty(max(sp[q], sp[o], sp[down]) * T * hidden, dtype=torch.float32, device="cuda")
+        z_gu = torch.empty(sp[gu] * T * 2 * inter, dtype=torch.float32, device="cuda")
+        scratch = torch.empty(1, dtype=torch.float32, device="cuda")
+        sv_h_scaled = (q.sv * 1e-3).contiguous()  # keeps the residual stream finite over the replays
+
+        def product(w, x, z):
+            if T == 1:
+                linear.qtip_multiply(w, x, z, w.n_out, sp[w], 1)
+            else:
+                linear.qtip_multiply_batch(w, x, z, w.n_out, sp[w], T)
+
+        def step():
+            linear.input_transform(state, norm1, eps, q.su, hidden, T, u_h, xn)
+            product(q, u_h, z_h)
+            linear.qtip_finish(q, z_h, y_q, scratch, False, sp[q], T)
+            for w in w8:
+                linear.fp8_forward(w, s8, xn, y_kv, hidden, kv, T)
+            linear.qtip_prepare(o, attn, scratch, u_o, T)
+            product(o, u_o, z_h)
+            linear.output_residual_input(z_h, sp[o], T, sv_h_scaled, hidden, state, norm2, eps, gate.su, u_h)
+            product(gu, u_h, z_gu)
+            linear.output_gateup(z_gu, sp[gu], T, gate.sv, up.sv, inter, h)
+            linear.qtip_prepare(down, h, scratch, u_d, T)
+            product(down, u_d, z_h)
+            linear.output_residual(z_h, sp[down], T, sv_h_scaled, hidden, state)
+
+        # the same step from the unfused operator stages, with the element-wise work as library kernels (one RMSNorm
+        # kernel, one add, SiLU and multiply), gate and up as two products: what a runtime without the epilogues launches
+        F = torch.nn.functional
+        y_h, y_g, y_u = y_q, torch.empty_like(h), torch.empty_like(h)
+        z_g = torch.empty(max(sp[gu], 1) * T * inter, dtype=torch.float32, device="cuda")
+        spl = {w: (linear.tc_splits(w.n_out) if T > 1 and linear.batch_uses_tc(w.n_in, w.n_out, T) else 1) for w in (gate, up)}
+
+        def product2(w, x, z):
+            if T == 1:
+                linear.qtip_multiply(w, x, z, w.n_out, spl[w], 1)
+            else:
+                linear.qtip_multiply_batch(w, x, z, w.n_out, spl[w], T)
+
+        def step_unfused():
+            xn.copy_(F.rms_norm(state, (hidden,), norm1, eps))
+            linear.qtip_prepare(q, xn, scratch, u_h, T)
+            product(q, u_h, z_h)
+            linear.qtip_finish(q, z_h, y_q, scratch, False, sp[q], T)
+            for w in w8:
+                linear.fp8_forward(w, s8, xn, y_kv, hidden, kv, T)
+            linear.qtip_prepare(o, attn, scratch, u_o, T)
+            product(o, u_o, z_h)
+            linear.qtip_finish(o, z_h, y_h, scratch, False, sp[o], T)
+            state.add_(y_h, alpha=1e-3)
+            xn.copy_(F.rms_norm(state, (hidden,), norm2, eps))
+            linear.qtip_prepare(gate, xn, scratch, u_h, T)
+            product2(gate, u_h, z_g)
+            linear.qtip_finish(gate, z_g, y_g, scratch, True, spl[gate], T)
+            product2(up, u_h, z_g)
+            linear.qtip_finish(up, z_g, y_u, scratch, True, spl[up], T)
+            torch.mul(F.silu(y_g), y_u, out=h)
+            linear.qtip_prepare(down, h, scratch, u_d, T)
+            product(down, u_d, z_h)
+            linear.qtip_finish(down, z_h, y_h, scratch, False, sp[down], T)
+            state.add_(y_h, alpha=1e-3)
+
+        fused_us = _graph_us(step, 2, torch)
+        ok = bool(torch.isfinite(state.float()).all()) and bool(torch.isfinite(h.float()).all())
+        out["T%d" % T] = {"step_us": fused_us, "unfused_step_us": _graph_us(step_unfused, 2, torch), "finite": ok}
+        del y_g, y_u, z_g
+        del state, attn, u_h, xn, u_o, y_q, h, u_d, z_h, z_gu
+    out["what"] = ("RMSNorm + input transform, q, FP8 k / v, o + residual + next norm and input transform, stacked "
+                   "gate|up + SiLU * up, down + residual; unfused_step_us: the same work from the operator's three stages with "
+                   "library kernels for norm, add and activation; layer_us above times the bare products")
+    return out
 
 
 
