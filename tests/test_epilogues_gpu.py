@@ -144,3 +144,40 @@ def test_output_residual_input_fused_equals_separate(gpu, n):
     lin.output_residual_input(z[:, :3].contiguous(), 2, 3, sv, n, st_c, norm, EPS, su, u_c)
     assert torch.equal(st_c.view(torch.int16), st_a[:3].view(torch.int16))
     assert torch.equal(u_c.view(torch.int16), u_a[:3].view(torch.int16))
+
+
+@pytest.mark.parametrize("n", [12288, 28672])
+def test_large_batch_row_kernels_match_the_chunk_kernels(gpu, n):
+    """Large batches (whole-row CTAs of 512 threads, several per SM) against the few-row chunk kernels on the same rows:
+    identical bits for the input transform, the output transform from fp32 products (with and without the bf16 rounding
+    of z) and the output transform from bf16 products."""
+    rows = 333  # more rows than SMs, not a multiple of anything
+    lin = gpu.linear
+    su, sv = dev(gpu.synth.signs(n, 7)), dev(gpu.synth.signs(n, 8)) * 0.01
+    w = lin.Matrix(None, su, sv, None, n, n)
+    scratch = torch.empty(1, device="cuda")
+    x = bf16_rows(rows, n, 3)
+    u_big = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda")
+    lin.qtip_prepare(w, x, scratch, u_big, rows)
+    pick = [0, 147, 148, rows - 1]
+    for r in pick:
+        u_one = torch.empty(1, n, dtype=torch.bfloat16, device="cuda")
+        lin.qtip_prepare(w, x[r:r + 1].contiguous(), scratch, u_one, 1)
+        assert torch.equal(u_big[r].view(torch.int16), u_one[0].view(torch.int16)), "input transform, row %d" % r
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4)
+    z = torch.randn(1, rows, n, generator=g, device="cuda")
+    for round_z in (False, True):
+        y_big = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda")
+        lin.qtip_finish(w, z, y_big, scratch, round_z, 1, rows)
+        for r in pick:
+            y_one = torch.empty(1, n, dtype=torch.bfloat16, device="cuda")
+            lin.qtip_finish(w, z[:, r:r + 1].contiguous(), y_one, scratch, round_z, 1, 1)
+            assert torch.equal(y_big[r].view(torch.int16), y_one[0].view(torch.int16)), "output transform, row %d" % r
+    zb = z[0].to(torch.bfloat16)
+    y_big = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda")
+    lin.qtip_finish_b16(w, zb, y_big, scratch, rows)
+    for r in pick:
+        y_one = torch.empty(1, n, dtype=torch.bfloat16, device="cuda")
+        lin.qtip_finish_b16(w, zb[r:r + 1].contiguous(), y_one, scratch, 1)
+        assert torch.equal(y_big[r].view(torch.int16), y_one[0].view(torch.int16)), "bf16 output transform, row %d" % r
